@@ -1,0 +1,258 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+The reference's runner contract has two calls for one request at a time,
+``prefill(ids[1,T], slot, start_position)`` and ``decode(ids[1,1], position, slot)``
+(src/infurnace/executor/runner.py:22-37), and its documents ask for the packed batch
+contract to be written down before it is built (docs/architecture.md:178-182).  This is
+that contract: a step is a list of entries; an entry is a live request, its next
+tokens (a whole prompt, a portion of one cut anywhere, or one decoded token) and the
+places among them whose logits are wanted.  All entries run as one batch on one flat
+token axis.  A step runs only the tokens it is given; everything earlier is read from
+the pages.
+
+What the kernels see of a step (all int32, on the device):
+
+* ``token_ids[N]``, ``positions[N]``: the tokens and their absolute positions;
+* ``cu_q[R+1]``: request r's tokens are rows cu_q[r] .. cu_q[r+1]-1;
+* ``seq_lens[R]``: request r's length after this step;
+* ``state_slots[R]``, ``first_portion[R]``: the request's row in fixed-size state
+  tensors, and whether this is the first step of its life;
+* per key/value group: ``slot_mapping[N]`` (page * page_size + offset of each token)
+  and ``block_tables[R, P]``;
+* ``logit_rows[M]``: the rows of the token axis whose logits are returned, in the order
+  of the entries and of their ``want`` lists.
+
+Order inside a layer: the step's keys and values are stored before attention reads
+(the write-before-read rule of docs/architecture.md:249-250), on one stream.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager, RELEASED
+from ..errors import BatchError, OutOfPages
+
+
+@dataclass
+class StepEntry:
+    request_id: str
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class KVView:
+    """What a mixer gets for its cache entry: the entry's pages and its group's tables."""
+    pages: torch.Tensor
+    block_tables: torch.Tensor
+    slot_mapping: torch.Tensor
+    page_size: int
+    window: Optional[int]
+
+
+class _Arena:
+    """Named device buffers that keep their address from step to step."""
+
+    def __init__(self, device, max_rows):
+        self.device, self.max_rows = device, max_rows
+        self._bufs: Dict[tuple, torch.Tensor] = {}
+
+    def get(self, name, shape, dtype, rows=None):
+        cap = max(rows or self.max_rows, shape[0])
+        key = (name, tuple(shape[1:]), dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.shape[0] < cap:
+            buf = torch.empty((cap, *shape[1:]), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[: shape[0]]
+
+
+class StepContext:
+    """One step as the parts see it."""
+
+    def __init__(self, runner: "ModelRunner"):
+        self._runner = runner
+        self.num_tokens = 0
+        self.num_requests = 0
+        self.num_logit_rows = 0
+        self.max_logit_rows = runner.max_tokens
+        self.max_q_len = 0
+        self.max_seq_len = 0
+        self.token_ids = self.positions = self.cu_q = self.seq_lens = None
+        self.state_slots = self.first_portion = self.logit_rows = self.req_index = None
+        self.group_slot_mapping: List[torch.Tensor] = []
+        self.group_block_tables: List[torch.Tensor] = []
+        # host copies, for parts written with torch operations
+        self.host_cu_q: List[int] = []
+        self.host_seq_lens: List[int] = []
+        self.host_state_slots: List[int] = []
+        self.host_first_portion: List[bool] = []
+
+    def buffer(self, name, shape, dtype, rows=None):
+        return self._runner.arena.get(name, shape, dtype, rows)
+
+    def kv(self, cache_id: int) -> KVView:
+        cache = self._runner.cache
+        gi = cache.kv_group_of(cache_id)
+        g = cache.kv_groups[gi]
+        return KVView(g.tensors[cache_id], self.group_block_tables[gi], self.group_slot_mapping[gi],
+                      g.page_size, g.need.window)
+
+    def state(self, cache_id: int) -> torch.Tensor:
+        """The fixed-size state tensor ``[slots, *shape]`` of a cache entry; request r of this
+        step owns row ``state_slots[r]``."""
+        cache = self._runner.cache
+        return cache.state_groups[cache.state_group_of(cache_id)].tensors[cache_id]
+
+
+class ModelRunner:
+    def __init__(self, model, cache: CacheManager, runtime, max_tokens: int, max_model_len: int):
+        self.model = model
+        self.cache = cache
+        self.rt = runtime
+        self.max_tokens = max_tokens
+        self.max_model_len = max_model_len
+        self.max_requests = cache.max_requests
+        self.max_pages = -(-max_model_len // cache.page_size)
+        self.arena = _Arena(runtime.device, max_tokens)
+        dev = runtime.device
+        self._pin = dev is not None and torch.device(dev).type == "cuda"
+        n, r, g = max_tokens, self.max_requests, len(cache.kv_groups)
+        # one staging area: [ids n][pos n][req n][logit_rows n][cu_q r+1][seq r][slot r][first r] + g * [slots n]
+        self._small_len = 4 * n + 4 * r + 1 + g * n
+        # two host staging sets used in turn: a set is rewritten only after the copy that
+        # read it last has finished (its event), so the host may run a step ahead
+        self._stage = [
+            (torch.zeros(self._small_len, dtype=torch.int32, pin_memory=self._pin),
+             torch.full((max(g, 1), r, self.max_pages), RELEASED, dtype=torch.int32, pin_memory=self._pin))
+            for _ in range(2)]
+        self._stage_events = [None, None]
+        self._dev_small = torch.zeros(self._small_len, dtype=torch.int32, device=dev)
+        self._dev_tables = torch.full((max(g, 1), r, self.max_pages), RELEASED, dtype=torch.int32, device=dev)
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ the step
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise BatchError("a step needs at least one entry")
+        if len(entries) > self.max_requests:
+            raise BatchError(f"{len(entries)} entries in a step; at most {self.max_requests}")
+        seen = set()
+        total = 0
+        vocab = self.model.plan.vocab_size
+        for e in entries:
+            if e.request_id in seen:
+                raise BatchError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if not self.cache.has_request(e.request_id):
+                raise BatchError(f"request {e.request_id!r} is not live; add it first")
+            n = len(e.tokens)
+            if n < 1:
+                raise BatchError(f"request {e.request_id!r} brings no tokens")
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise BatchError(f"token id {t} of request {e.request_id!r} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise BatchError(f"request {e.request_id!r} wants logits at place {w} of {n} tokens")
+            if self.cache.num_computed(e.request_id) + n > self.max_model_len:
+                raise BatchError(f"request {e.request_id!r} would grow past max_model_len {self.max_model_len}")
+            total += n
+        if total > self.max_tokens:
+            raise BatchError(f"{total} tokens in a step; at most {self.max_tokens}")
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns float32 logits ``[wanted, vocab]`` on the device (None if
+        nothing is wanted).  The returned tensor is a buffer that the next step overwrites.
+
+        Raises :class:`OutOfPages`, with nothing changed, if the pages for the step's tokens
+        cannot all be had."""
+        self.validate(entries)
+        cache = self.cache
+        done = []
+        try:
+            for e in entries:
+                cache.allocate(e.request_id, len(e.tokens))
+                done.append(e)
+        except OutOfPages:
+            for e in done:
+                cache.release_allocation(e.request_id)
+            raise
+        ctx = self._build_context(entries)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            cache.commit(e.request_id, len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    # ------------------------------------------------------------------ metadata
+    def _build_context(self, entries) -> StepContext:
+        cache = self.cache
+        n_max, r_max = self.max_tokens, self.max_requests
+        turn = self.steps_run % 2
+        if self._stage_events[turn] is not None:
+            self._stage_events[turn].synchronize()
+        host_small, host_tables = self._stage[turn]
+        ids, pos, req, rows, cu, seq, slots, first = [], [], [], [], [0], [], [], []
+        group_slots = [[] for _ in cache.kv_groups]
+        max_q = 0
+        for r, e in enumerate(entries):
+            start = cache.num_computed(e.request_id)
+            n = len(e.tokens)
+            base = len(ids)
+            ids.extend(int(t) for t in e.tokens)
+            pos.extend(range(start, start + n))
+            req.extend([r] * n)
+            rows.extend(base + int(w) for w in e.want)
+            cu.append(base + n)
+            seq.append(start + n)
+            slots.append(cache.slot_of(e.request_id))
+            first.append(1 if start == 0 else 0)
+            max_q = max(max_q, n)
+            for gi in range(len(cache.kv_groups)):
+                group_slots[gi].extend(cache.slots_for(e.request_id, gi, n))
+                table = cache.block_table(e.request_id, gi)
+                row = host_tables[gi, r]
+                row[: len(table)] = torch.tensor(table, dtype=torch.int32)
+        N, R, M = len(ids), len(entries), len(rows)
+        h = host_small
+        o_ids, o_pos, o_req, o_rows = 0, n_max, 2 * n_max, 3 * n_max
+        o_cu = 4 * n_max
+        o_seq = o_cu + r_max + 1
+        o_slot = o_seq + r_max
+        o_first = o_slot + r_max
+        o_g = o_first + r_max
+        h[o_ids:o_ids + N] = torch.tensor(ids, dtype=torch.int32)
+        h[o_pos:o_pos + N] = torch.tensor(pos, dtype=torch.int32)
+        h[o_req:o_req + N] = torch.tensor(req, dtype=torch.int32)
+        if M:
+            h[o_rows:o_rows + M] = torch.tensor(rows, dtype=torch.int32)
+        h[o_cu:o_cu + R + 1] = torch.tensor(cu, dtype=torch.int32)
+        h[o_seq:o_seq + R] = torch.tensor(seq, dtype=torch.int32)
+        h[o_slot:o_slot + R] = torch.tensor(slots, dtype=torch.int32)
+        h[o_first:o_first + R] = torch.tensor(first, dtype=torch.int32)
+        for gi, gs in enumerate(group_slots):
+            h[o_g + gi * n_max: o_g + gi * n_max + N] = torch.tensor(gs, dtype=torch.int32)
+        d = self._dev_small
+        d.copy_(h, non_blocking=True)
+        if cache.kv_groups:
+            self._dev_tables[:, :R].copy_(host_tables[:, :R], non_blocking=True)
+        if self._pin:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._stage_events[turn] = ev
+        ctx = StepContext(self)
+        ctx.num_tokens, ctx.num_requests, ctx.num_logit_rows = N, R, M
+        ctx.max_q_len, ctx.max_seq_len = max_q, max(seq)
+        ctx.token_ids, ctx.positions = d[o_ids:o_ids + N], d[o_pos:o_pos + N]
+        ctx.req_index, ctx.logit_rows = d[o_req:o_req + N], d[o_rows:o_rows + M]
+        ctx.cu_q, ctx.seq_lens = d[o_cu:o_cu + R + 1], d[o_seq:o_seq + R]
+        ctx.state_slots, ctx.first_portion = d[o_slot:o_slot + R], d[o_first:o_first + R]
+        ctx.group_slot_mapping = [d[o_g + gi * n_max: o_g + gi * n_max + N] for gi in range(len(cache.kv_groups))]
+        ctx.group_block_tables = [self._dev_tables[gi, :R] for gi in range(len(cache.kv_groups))]
+        ctx.host_cu_q, ctx.host_seq_lens = cu, seq
+        ctx.host_state_slots, ctx.host_first_portion = slots, [bool(f) for f in first]
+        return ctx

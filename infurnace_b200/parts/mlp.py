@@ -1,0 +1,34 @@
+"""The dense gated feed-forward."""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import GatedMLPSpec
+from ..errors import ModelConfigError
+from .registry import register_part
+
+
+class GatedMLP:
+    """down(silu(gate(h)) * up(h)) (src/infurnace/executor/tinygrad/model.py:146-148).
+    gate and up run as one product against their row-wise concatenation (exact), with the
+    activation and the product of the two halves in that kernel's epilogue."""
+
+    def __init__(self, spec: GatedMLPSpec, weights, runtime):
+        if spec.activation != "silu":
+            raise ModelConfigError(f"activation {spec.activation!r}: only 'silu' has a kernel")
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.w_gate_up = torch.cat((weights[spec.gate_proj], weights[spec.up_proj]), dim=0).contiguous()
+        self.w_down = weights[spec.down_proj]
+
+    def forward(self, h, ctx):
+        n = h.shape[0]
+        act = ctx.buffer("ffn_act", (n, self.spec.intermediate_size), self.rt.act_dtype)
+        self.k.linear(h, self.w_gate_up, act, epilogue="silu_gate")
+        delta = ctx.buffer("delta_ffn", (n, self.spec.hidden_size), torch.float32)
+        self.k.linear(act, self.w_down, delta)
+        return delta
+
+
+register_part(GatedMLPSpec, GatedMLP)

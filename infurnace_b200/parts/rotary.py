@@ -1,0 +1,34 @@
+"""Rotary position encoding."""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import RotarySpec
+from ..errors import ModelConfigError
+from .registry import register_part
+
+
+class Rotary:
+    """inv_freq_i = 1 / theta^(2i / rotary_dim), angle = position * inv_freq_i, both in
+    float32 (src/infurnace/executor/tinygrad/model.py:18-22); the rotation itself runs
+    inside the attention part's fused kernel, which takes the frequencies, the rotated
+    width and the pairing as arguments (model.py:24-27 is the half-split pairing)."""
+
+    def __init__(self, spec: RotarySpec, weights, runtime):
+        if spec.rotary_dim % 2 or not 0 < spec.rotary_dim <= spec.head_dim:
+            raise ModelConfigError(f"rotary_dim {spec.rotary_dim} must be even and at most head_dim {spec.head_dim}")
+        self.spec = spec
+        self.k = runtime.kernels
+        exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32) / spec.rotary_dim
+        self.inv_freq = (1.0 / (spec.theta ** exponent)).to(runtime.device)
+
+    def fused_rotary(self):
+        return self.inv_freq, self.spec.rotary_dim, self.spec.interleaved
+
+    def apply(self, qkv, num_heads, num_kv_heads, head_dim, positions):
+        self.k.qk_norm_rope_store(qkv, num_heads, num_kv_heads, head_dim, None, None, 0.0,
+                                  self.inv_freq, self.spec.rotary_dim, self.spec.interleaved,
+                                  positions, None, None)
+
+
+register_part(RotarySpec, Rotary)
