@@ -1,0 +1,236 @@
+// Embedding gather, RMSNorm with the residual addition, fused q/k norm + rotation + paged
+// store, and sampling.  These kernels take every size: widths, head sizes and vocabularies
+// need not be powers of two or multiples of anything (head_dim even when rotated).
+#include "common.cuh"
+#include <math.h>
+
+// ------------------------------------------------------------------------------------------
+// embed: out[n, :] = float(table[ids[n], :])
+// ------------------------------------------------------------------------------------------
+__global__ void embed_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ ids,
+                             float* __restrict__ out, int hidden) {
+  const int n = blockIdx.x;
+  const size_t row = (size_t)ids[n] * hidden;
+  for (int h = threadIdx.x; h < hidden; h += blockDim.x)
+    out[(size_t)n * hidden + h] = load_as_f32(table, table_dtype, row + h);
+}
+
+IFB_EXPORT int ifb_embed(const void* table, int table_dtype, const int* ids, float* out, int n, int hidden,
+                         cudaStream_t stream) {
+  if (n <= 0) return IFB_OK;
+  if (table_dtype != IFB_F32 && table_dtype != IFB_BF16) return IFB_ERR_DTYPE;
+  embed_kernel<<<n, 256, 0, stream>>>(table, table_dtype, ids, out, hidden);
+  return ifb_launch_status();
+}
+
+// ------------------------------------------------------------------------------------------
+// rmsnorm: v = x[row] + sum_s delta[s][row];  out = v * rsqrt(mean(v^2) + eps) * w
+// Without `rows`, row = blockIdx.x and v is written back to x.  With `rows`, row = rows[blockIdx.x]
+// and x stays as it is.  One block per output row; v is kept in shared memory between the passes.
+// ------------------------------------------------------------------------------------------
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int num_splits,
+                               size_t split_stride, const void* __restrict__ w, int w_dtype, float eps,
+                               void* __restrict__ out, int out_dtype, const int* __restrict__ rows, int hidden) {
+  extern __shared__ float vbuf[];
+  __shared__ float scratch[33];
+  const int orow = blockIdx.x;
+  const int row = rows ? rows[orow] : orow;
+  float* xr = x + (size_t)row * hidden;
+  float ss = 0.f;
+  for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+    float v = xr[h];
+    for (int s = 0; s < num_splits; ++s) v += delta[(size_t)s * split_stride + (size_t)row * hidden + h];
+    vbuf[h] = v;
+    if (!rows && num_splits) xr[h] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float r = rsqrtf(ss / (float)hidden + eps);
+  for (int h = threadIdx.x; h < hidden; h += blockDim.x)
+    store_from_f32(out, out_dtype, (size_t)orow * hidden + h, vbuf[h] * r * load_as_f32(w, w_dtype, h));
+}
+
+IFB_EXPORT int ifb_rmsnorm(float* x, const float* delta, int num_splits, long long split_stride, const void* w,
+                           int w_dtype, float eps, void* out, int out_dtype, const int* rows, int num_out_rows,
+                           int hidden, cudaStream_t stream) {
+  if (num_out_rows <= 0) return IFB_OK;
+  if ((w_dtype != IFB_F32 && w_dtype != IFB_BF16) || (out_dtype != IFB_F32 && out_dtype != IFB_BF16)) return IFB_ERR_DTYPE;
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem > 200 * 1024) return IFB_ERR_SIZE;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return -(int)e;
+    configured = smem;
+  }
+  const int threads = hidden >= 2048 ? 512 : 256;
+  rmsnorm_kernel<<<num_out_rows, threads, smem, stream>>>(x, delta, delta ? num_splits : 0, (size_t)split_stride, w,
+                                                          w_dtype, eps, out, out_dtype, rows, hidden);
+  return ifb_launch_status();
+}
+
+// ------------------------------------------------------------------------------------------
+// qk_norm_rope_store: one warp per (token, head) of the fused qkv row [q heads | k heads | v heads].
+//   q, k heads: optional RMSNorm over the head (weight shared by all heads), optional rotation of
+//   the first rotary_dim elements by angle position * inv_freq[i]; written back in place.
+//   k, v heads: stored to the page slot of the token, [page][k|v][kv_head][offset][d], when slot >= 0.
+// Statistics, angles and the rotation are float32; sincosf is the accurate routine.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv, int d,
+                                          const void* __restrict__ qw, const void* __restrict__ kw, int w_dtype,
+                                          float eps, const float* __restrict__ inv_freq, int rotary_dim,
+                                          int interleaved, const int* __restrict__ positions,
+                                          const int* __restrict__ slots, T* __restrict__ pages, int page_size) {
+  extern __shared__ float sm[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= (long long)n_tokens * heads) return;
+  const int tok = (int)(item / heads), head = (int)(item % heads);
+  float* buf = sm + (size_t)warp * d;
+  T* src = qkv + (size_t)tok * heads * d + (size_t)head * d;
+  const bool is_v = head >= nq + nkv, is_k = head >= nq && !is_v;
+  const void* w = is_v ? nullptr : (is_k ? kw : qw);
+  const bool rotate = !is_v && inv_freq != nullptr;
+  const int slot = (slots && head >= nq) ? slots[tok] : -1;
+  if (is_v) {
+    if (slot >= 0) {
+      const int kvh = head - nq - nkv;
+      T* dst = pages + ((((size_t)(slot / page_size) * 2 + 1) * nkv + kvh) * page_size + (slot % page_size)) * d;
+      for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    }
+    return;
+  }
+  if (!w && !rotate && slot < 0) return;
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) { float v = to_f32<T>(src[i]); buf[i] = v; ss += v * v; }
+  if (w) {
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)d + eps);
+    __syncwarp();
+    for (int i = lane; i < d; i += 32) buf[i] = buf[i] * r * load_as_f32(w, w_dtype, i);
+  }
+  __syncwarp();
+  T* dst = nullptr;
+  if (slot >= 0) {
+    const int kvh = head - nq;
+    dst = pages + ((((size_t)(slot / page_size) * 2 + 0) * nkv + kvh) * page_size + (slot % page_size)) * d;
+  }
+  const float pos = rotate ? (float)positions[tok] : 0.f;
+  const int half = rotary_dim >> 1;
+  for (int i = lane; i < d; i += 32) {
+    float v = buf[i];
+    if (rotate && i < rotary_dim) {
+      int pair, fi; bool first;
+      if (interleaved) { first = (i & 1) == 0; pair = first ? i + 1 : i - 1; fi = i >> 1; }
+      else { first = i < half; pair = first ? i + half : i - half; fi = first ? i : i - half; }
+      float s, c;
+      sincosf(pos * inv_freq[fi], &s, &c);
+      const float o = buf[pair];
+      v = first ? v * c - o * s : v * c + o * s;
+    }
+    const T t = from_f32<T>(v);
+    if (w || rotate) src[i] = t;
+    if (dst) dst[i] = t;
+  }
+}
+
+IFB_EXPORT int ifb_qk_norm_rope_store(void* qkv, int dtype, int n_tokens, int nq, int nkv, int d, const void* qw,
+                                      const void* kw, int w_dtype, float eps, const float* inv_freq, int rotary_dim,
+                                      int interleaved, const int* positions, const int* slots, void* pages,
+                                      int page_size, cudaStream_t stream) {
+  if (n_tokens <= 0) return IFB_OK;
+  if (d < 1 || d > 1024) return IFB_ERR_SIZE;
+  if (inv_freq && (rotary_dim < 2 || rotary_dim > d || (rotary_dim & 1) || !positions)) return IFB_ERR_ARG;
+  if (slots && (!pages || page_size < 1)) return IFB_ERR_ARG;
+  if ((qw || kw) && w_dtype != IFB_F32 && w_dtype != IFB_BF16) return IFB_ERR_DTYPE;
+  const int warps = 4;
+  const long long items = (long long)n_tokens * (nq + 2 * nkv);
+  const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+  const size_t smem = (size_t)warps * d * sizeof(float);
+  if (dtype == IFB_F32)
+    qk_norm_rope_store_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+        (float*)qkv, n_tokens, nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rotary_dim, interleaved, positions, slots,
+        (float*)pages, page_size);
+  else if (dtype == IFB_BF16)
+    qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+        (__nv_bfloat16*)qkv, n_tokens, nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rotary_dim, interleaved, positions,
+        slots, (__nv_bfloat16*)pages, page_size);
+  else
+    return IFB_ERR_DTYPE;
+  return ifb_launch_status();
+}
+
+// ------------------------------------------------------------------------------------------
+// sample: one block per row of float32 logits.
+//   temperature == 0: index of the largest logit, the lowest index among equals.
+//   else: smallest i with sum_{j<=i} exp((l_j - max)/T) > u * sum_j exp((l_j - max)/T).
+// Each thread owns a contiguous chunk of the row, so the running sum follows index order.
+// ------------------------------------------------------------------------------------------
+__global__ void sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+                              const float* __restrict__ uniform, int* __restrict__ out) {
+  __shared__ float scratch[33];
+  __shared__ float sums[1024];
+  __shared__ int best_idx[32];
+  __shared__ float best_val[32];
+  __shared__ int chosen;
+  const int row = blockIdx.x, tid = threadIdx.x, nthreads = blockDim.x;
+  const float* l = logits + (size_t)row * vocab;
+  const float temp = temperature ? temperature[row] : 0.f;
+  const int chunk = (vocab + nthreads - 1) / nthreads;
+  const int begin = min(vocab, tid * chunk), end = min(vocab, begin + chunk);
+  // the largest value and its lowest index
+  float bv = -INFINITY; int bi = 0x7fffffff;
+  for (int i = begin; i < end; ++i) { float v = l[i]; if (v > bv) { bv = v; bi = i; } }
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if ((tid & 31) == 0) { best_val[tid >> 5] = bv; best_idx[tid >> 5] = bi; }
+  __syncthreads();
+  if (tid < 32) {
+    const int nw = (nthreads + 31) >> 5;
+    bv = tid < nw ? best_val[tid] : -INFINITY; bi = tid < nw ? best_idx[tid] : 0x7fffffff;
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (tid == 0) { best_val[0] = bv; best_idx[0] = bi; }
+  }
+  __syncthreads();
+  const float mx = best_val[0];
+  if (temp == 0.f) { if (tid == 0) out[row] = best_idx[0]; return; }
+  const float inv_t = 1.f / temp;
+  float part = 0.f;
+  for (int i = begin; i < end; ++i) part += expf((l[i] - mx) * inv_t);
+  sums[tid] = part;
+  const float total = block_sum(part, scratch);
+  const float target = uniform[row] * total;
+  if (tid == 0) {
+    // walk the chunk sums in index order, then the elements of the chunk that crosses the target
+    float run = 0.f; int t = 0;
+    for (; t < nthreads; ++t) { if (run + sums[t] > target) break; run += sums[t]; }
+    int pick = -1;
+    if (t < nthreads) {
+      const int b = min(vocab, t * chunk), e = min(vocab, b + chunk);
+      for (int i = b; i < e; ++i) { run += expf((l[i] - mx) * inv_t); if (run > target) { pick = i; break; } }
+      if (pick < 0) pick = e - 1;
+    }
+    if (pick < 0) {   // rounding left the target unreached: the last index with non-zero weight
+      pick = best_idx[0];
+      for (int i = vocab - 1; i >= 0; --i) if (expf((l[i] - mx) * inv_t) > 0.f) { pick = i; break; }
+    }
+    chosen = pick;
+  }
+  __syncthreads();
+  if (tid == 0) out[row] = chosen;
+}
+
+IFB_EXPORT int ifb_sample(const float* logits, int rows, int vocab, const float* temperature, const float* uniform,
+                          int* out, cudaStream_t stream) {
+  if (rows <= 0) return IFB_OK;
+  if (vocab < 1) return IFB_ERR_SIZE;
+  sample_kernel<<<rows, 1024, 0, stream>>>(logits, vocab, temperature, uniform, out);
+  return ifb_launch_status();
+}

@@ -1,0 +1,137 @@
+"""Compiling and loading the CUDA kernel libraries.
+
+Each library is a few ``.cu`` files under ``infurnace_b200/csrc`` compiled by ``nvcc`` for
+sm_100a into one shared object with plain C entry points, loaded with ``ctypes``.  The
+object's file name carries a hash of its sources and flags, so an edited source is
+rebuilt and a stale object is never loaded.  Objects live in ``infurnace_b200/_build``
+(or, if that folder cannot be written, in a per-user folder under the system's temporary
+directory).  A library is compiled at its first use; while the compiler runs, a line is
+printed every few seconds.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from typing import Dict, List, Optional, Sequence
+
+from ..errors import KernelError
+
+CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+
+# library name -> (sources, extra flags)
+LIBRARIES: Dict[str, tuple] = {
+    "core": (["elementwise.cu", "linear_simt.cu", "attention_simt.cu"], []),
+}
+
+_loaded: Dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+def _say(progress, msg):
+    if progress is not None:
+        progress(msg)
+    else:
+        print(f"[infurnace_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("INFURNACE_NVCC"), shutil.which("nvcc"),
+                 os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")):
+        if cand and os.path.exists(cand):
+            return cand
+    raise KernelError("nvcc was not found (PATH, CUDA_HOME, /usr/local/cuda): the CUDA kernels cannot be compiled")
+
+
+def build_dir() -> str:
+    d = os.path.join(os.path.dirname(CSRC), "_build")
+    try:
+        os.makedirs(d, exist_ok=True)
+        probe = os.path.join(d, f".w{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return d
+    except OSError:
+        d = os.path.join(tempfile.gettempdir(), f"infurnace_b200-build-{os.getuid()}")
+        os.makedirs(d, exist_ok=True)
+        return d
+
+
+def _hash(sources: Sequence[str], flags: Sequence[str]) -> str:
+    h = hashlib.sha256()
+    headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+    for name in list(sources) + headers:
+        with open(os.path.join(CSRC, name), "rb") as f:
+            h.update(name.encode() + b"\0" + f.read())
+    h.update(" ".join(list(ARCH_FLAGS) + list(BASE_FLAGS) + list(flags)).encode())
+    return h.hexdigest()[:16]
+
+
+def library_path(name: str, defines: Optional[Dict[str, object]] = None) -> str:
+    sources, flags = LIBRARIES[name]
+    flags = list(flags) + [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
+    tag = "".join(f"_{k.lower()}{v}" for k, v in sorted((defines or {}).items()))
+    return os.path.join(build_dir(), f"libifb_{name}{tag}-{_hash(sources, flags)}.so")
+
+
+def compile_library(name: str, defines: Optional[Dict[str, object]] = None, progress=None) -> str:
+    """Compile if the object for the current sources is absent.  Returns its path."""
+    path = library_path(name, defines)
+    if os.path.exists(path):
+        return path
+    sources, flags = LIBRARIES[name]
+    flags = list(flags) + [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
+    tmp = f"{path}.{os.getpid()}.tmp"
+    cmd = [find_nvcc(), *ARCH_FLAGS, *BASE_FLAGS, *flags, "-I", CSRC, "-o", tmp,
+           *[os.path.join(CSRC, s) for s in sources]]
+    label = os.path.basename(path)
+    _say(progress, f"compiling {label} ({len(sources)} source files) with nvcc ...")
+    t0 = time.monotonic()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    out: List[str] = []
+    reader = threading.Thread(target=lambda: out.append(proc.stdout.read()), daemon=True)
+    reader.start()
+    while True:
+        try:
+            proc.wait(timeout=10)
+            break
+        except subprocess.TimeoutExpired:
+            _say(progress, f"still compiling {label} ({time.monotonic() - t0:.0f} s)")
+    reader.join()
+    if proc.returncode != 0:
+        try:
+            os.remove(tmp)
+        except OSError:
+            pass
+        raise KernelError(f"nvcc failed on {label}:\n{''.join(out)[-4000:]}")
+    os.replace(tmp, path)
+    _say(progress, f"compiled {label} in {time.monotonic() - t0:.1f} s")
+    return path
+
+
+def load_library(name: str, defines: Optional[Dict[str, object]] = None, progress=None) -> ctypes.CDLL:
+    key = name + repr(sorted((defines or {}).items()))
+    with _lock:
+        lib = _loaded.get(key)
+        if lib is None:
+            path = compile_library(name, defines, progress)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load {path}: {e}") from None
+            _loaded[key] = lib
+        return lib
+
+
+def build_all(progress=None) -> List[str]:
+    """Compile every library (used by the build check; needs no GPU)."""
+    return [compile_library(name, None, progress) for name in LIBRARIES]

@@ -1,0 +1,188 @@
+"""The CUDA kernel set: thin, checked calls into the compiled libraries.
+
+Every method takes device tensors, checks what the kernel assumes (dtype, contiguity,
+matching sizes) and launches on torch's current stream.  There is no CPU path: without
+a CUDA device or without the compiled library the constructor raises
+:class:`~infurnace_b200.errors.KernelError`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..errors import KernelError
+from .build import load_library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+_ERRORS = {1: "a dtype (or combination of dtypes) has no kernel", 2: "a size is outside what the kernel takes",
+           3: "an address or row length breaks the kernel's alignment rule", 4: "arguments contradict each other"}
+
+
+def _code(t):
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} has no kernel; float32 and bfloat16 do") from None
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _check(status, what):
+    if status == 0:
+        return
+    if status > 0:
+        raise KernelError(f"{what}: refused: {_ERRORS.get(status, status)}")
+    raise KernelError(f"{what}: CUDA launch failed with error {-status}")
+
+
+def _dense(t, name, dtype=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name} is not on a CUDA device")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    return t
+
+
+class CudaKernels:
+    name = "cuda"
+
+    def __init__(self, progress=None):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device is available; this engine has no CPU path")
+        self._progress = progress
+        self.core = load_library("core", progress=progress)
+        c = self.core
+        c.ifb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        c.ifb_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_void_p, c_int,
+                                  c_void_p, c_int, c_int, c_void_p]
+        c.ifb_qk_norm_rope_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                             c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_void_p]
+        c.ifb_sample.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+        c.ifb_linear_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                      c_void_p]
+        c.ifb_paged_attention_simt.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                               c_void_p]
+
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    # ------------------------------------------------------------------ embedding
+    def embed(self, table, ids, out):
+        _dense(table, "table"), _dense(ids, "ids", torch.int32), _dense(out, "out", torch.float32)
+        n, hidden = out.shape
+        if table.shape[1] != hidden or ids.numel() != n:
+            raise KernelError("embed: sizes of table, ids and out do not match")
+        _check(self.core.ifb_embed(table.data_ptr(), _code(table), ids.data_ptr(), out.data_ptr(), n, hidden,
+                                   self._stream()), "embed")
+
+    # ------------------------------------------------------------------ norm
+    def rmsnorm(self, x, weight, eps, out, delta=None, rows=None):
+        _dense(x, "x", torch.float32), _dense(weight, "weight"), _dense(out, "out")
+        hidden = x.shape[1]
+        n_out = out.shape[0]
+        if weight.numel() != hidden or out.shape[1] != hidden:
+            raise KernelError("rmsnorm: widths of x, weight and out do not match")
+        splits, stride = 0, 0
+        if delta is not None:
+            _dense(delta, "delta", torch.float32)
+            if delta.dim() == 3:
+                splits, stride = delta.shape[0], delta.stride(0)
+                drows = delta.shape[1]
+            else:
+                splits, stride, drows = 1, 0, delta.shape[0]
+            if delta.shape[-1] != hidden or drows != x.shape[0]:
+                raise KernelError("rmsnorm: delta does not match x")
+        if rows is not None:
+            _dense(rows, "rows", torch.int32)
+            if rows.numel() != n_out:
+                raise KernelError("rmsnorm: out has a row for each entry of rows")
+        elif n_out != x.shape[0]:
+            raise KernelError("rmsnorm: out has a row for each row of x")
+        _check(self.core.ifb_rmsnorm(x.data_ptr(), _ptr(delta), splits, stride, weight.data_ptr(), _code(weight),
+                                     float(eps), out.data_ptr(), _code(out), _ptr(rows), n_out, hidden,
+                                     self._stream()), "rmsnorm")
+
+    # ------------------------------------------------------------------ matrix products
+    def linear(self, x, w, out, epilogue="none"):
+        _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
+        n, k = x.shape
+        o = out.shape[1]
+        epi = {"none": 0, "silu_gate": 1}[epilogue]
+        if w.shape[1] != k or out.shape[0] != n or w.shape[0] != (2 * o if epi else o):
+            raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not match")
+        _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
+                                         n, o, k, epi, self._stream()), "linear")
+
+    # ------------------------------------------------------------------ q/k norm, rotation, store
+    def qk_norm_rope_store(self, qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, inv_freq,
+                           rotary_dim, interleaved, positions, slot_mapping, kv_pages):
+        _dense(qkv, "qkv")
+        n = qkv.shape[0]
+        if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+            raise KernelError("qk_norm_rope_store: qkv width is not (heads + 2 kv_heads) * head_dim")
+        wd = F32
+        for wt in (q_weight, k_weight):
+            if wt is not None:
+                _dense(wt, "norm weight")
+                if wt.numel() != head_dim:
+                    raise KernelError("qk_norm_rope_store: norm weight length is not head_dim")
+                wd = _code(wt)
+        if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
+            raise KernelError("qk_norm_rope_store: q and k norm weights differ in dtype")
+        if inv_freq is not None:
+            _dense(inv_freq, "inv_freq", torch.float32), _dense(positions, "positions", torch.int32)
+            if inv_freq.numel() != rotary_dim // 2 or positions.numel() != n:
+                raise KernelError("qk_norm_rope_store: inv_freq or positions has the wrong length")
+        page_size = 1
+        if slot_mapping is not None:
+            _dense(slot_mapping, "slot_mapping", torch.int32), _dense(kv_pages, "kv_pages", qkv.dtype)
+            if kv_pages.dim() != 5 or kv_pages.shape[1] != 2 or kv_pages.shape[2] != num_kv_heads \
+                    or kv_pages.shape[4] != head_dim or slot_mapping.numel() != n:
+                raise KernelError("qk_norm_rope_store: kv_pages is not [pages, 2, kv_heads, page_size, head_dim]")
+            page_size = kv_pages.shape[3]
+        _check(self.core.ifb_qk_norm_rope_store(
+            qkv.data_ptr(), _code(qkv), n, num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight), wd,
+            float(eps), _ptr(inv_freq), int(rotary_dim), int(bool(interleaved)), _ptr(positions), _ptr(slot_mapping),
+            _ptr(kv_pages) if slot_mapping is not None else 0, page_size, self._stream()), "qk_norm_rope_store")
+
+    # ------------------------------------------------------------------ attention
+    def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out,
+                        scale, window, max_q_len, max_seq_len):
+        _dense(qkv, "qkv"), _dense(kv_pages, "kv_pages", qkv.dtype), _dense(out, "out", qkv.dtype)
+        _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
+        if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
+            raise KernelError("paged_attention: block_tables must be int32 with unit stride along pages")
+        n = qkv.shape[0]
+        r = seq_lens.numel()
+        if cu_q.numel() != r + 1 or block_tables.shape[0] < r or out.shape != (n, num_heads * head_dim):
+            raise KernelError("paged_attention: sizes of cu_q, seq_lens, block_tables and out do not match")
+        if kv_pages.dim() != 5 or kv_pages.shape[1] != 2 or kv_pages.shape[2] != num_kv_heads \
+                or kv_pages.shape[4] != head_dim:
+            raise KernelError("paged_attention: kv_pages is not [pages, 2, kv_heads, page_size, head_dim]")
+        _check(self.core.ifb_paged_attention_simt(
+            qkv.data_ptr(), _code(qkv), qkv.stride(0), kv_pages.data_ptr(), block_tables.data_ptr(),
+            block_tables.stride(0), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), n, r, num_heads,
+            num_kv_heads, head_dim, kv_pages.shape[3], float(scale), int(window), self._stream()), "paged_attention")
+
+    # ------------------------------------------------------------------ sampling
+    def sample(self, logits, temperature, uniform, out):
+        _dense(logits, "logits", torch.float32), _dense(out, "out", torch.int32)
+        m, vocab = logits.shape
+        if temperature is not None:
+            _dense(temperature, "temperature", torch.float32), _dense(uniform, "uniform", torch.float32)
+            if temperature.numel() != m or uniform.numel() != m:
+                raise KernelError("sample: one temperature and one uniform number per row")
+        if out.numel() != m:
+            raise KernelError("sample: out has one entry per row")
+        _check(self.core.ifb_sample(logits.data_ptr(), m, vocab, _ptr(temperature), _ptr(uniform), out.data_ptr(),
+                                    self._stream()), "sample")

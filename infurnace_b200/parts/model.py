@@ -63,8 +63,8 @@ class DecoderModel:
         m = ctx.num_logit_rows
         if m == 0:
             return None
-        hn = ctx.buffer("h_final", (m, self.plan.hidden_size), self.rt.act_dtype, rows=ctx.max_logit_rows)
+        hn = ctx.buffer("h_final", (m, self.plan.hidden_size), self.rt.act_dtype, rows=m)
         self.final_norm.forward(x, hn, delta=pending, rows=ctx.logit_rows)
-        logits = ctx.buffer("logits", (m, self.plan.vocab_size), torch.float32, rows=ctx.max_logit_rows)
+        logits = ctx.buffer("logits", (m, self.plan.vocab_size), torch.float32, rows=m)
         self.lm_head.forward(hn, logits)
         return logits

@@ -1,0 +1,206 @@
+"""Each CUDA kernel alone against its plain statement (tests/kernel_refs.py), at sizes other
+than the engine's: widths, head sizes, vocabularies and page sizes that are no powers of two."""
+import math
+
+import pytest
+import torch
+
+from kernel_refs import ReferenceKernels
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def K():
+    from infurnace_b200.kernels import load_cuda_kernels
+    return load_cuda_kernels()
+
+
+REF = ReferenceKernels(torch.float64)
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-3)
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,hidden,vocab", [(1, 72, 333), (37, 1000, 129)])
+def test_embed(K, dtype, n, hidden, vocab):
+    table = rnd((vocab, hidden), dtype, 0)
+    ids = torch.randint(0, vocab, (n,), dtype=torch.int32)
+    ids[-1] = vocab - 1
+    out = torch.empty((n, hidden), dtype=torch.float32, device="cuda")
+    K.embed(table.cuda(), ids.cuda(), out)
+    assert torch.equal(out.cpu(), table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("n,hidden,splits", [(1, 72, 0), (5, 1000, 1), (33, 3001, 3)])
+def test_rmsnorm(K, dtype, wdtype, n, hidden, splits):
+    x = rnd((n, hidden), torch.float32, 1)
+    w = (1 + 0.1 * rnd((hidden,), torch.float32, 2)).to(wdtype)
+    delta = None if splits == 0 else rnd((n, hidden) if splits == 1 else (splits, n, hidden), torch.float32, 3)
+    # without rows: x is updated
+    x_ref, out_ref = x.clone(), torch.empty((n, hidden), dtype=dtype)
+    REF.rmsnorm(x_ref, w, 1e-5, out_ref, delta=delta)
+    x_gpu, out_gpu = x.cuda(), torch.empty((n, hidden), dtype=dtype, device="cuda")
+    K.rmsnorm(x_gpu, w.cuda(), 1e-5, out_gpu, delta=None if delta is None else delta.cuda())
+    torch.testing.assert_close(x_gpu.cpu(), x_ref, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(out_gpu.cpu().float(), out_ref.float(), **tol(dtype))
+    # with rows: x is left alone
+    rows = torch.tensor([n - 1, 0, n // 2], dtype=torch.int32)
+    out_ref = torch.empty((3, hidden), dtype=dtype)
+    REF.rmsnorm(x.clone(), w, 1e-5, out_ref, delta=delta, rows=rows)
+    x_gpu, out_gpu = x.cuda(), torch.empty((3, hidden), dtype=dtype, device="cuda")
+    K.rmsnorm(x_gpu, w.cuda(), 1e-5, out_gpu, delta=None if delta is None else delta.cuda(), rows=rows.cuda())
+    assert torch.equal(x_gpu.cpu(), x)
+    torch.testing.assert_close(out_gpu.cpu().float(), out_ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("xd,wd,od", [(torch.float32, torch.float32, torch.float32),
+                                      (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                      (torch.bfloat16, torch.bfloat16, torch.float32),
+                                      (torch.bfloat16, torch.float32, torch.bfloat16),
+                                      (torch.float32, torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("n,o,k", [(1, 72, 72), (7, 333, 136), (130, 200, 1000), (64, 64, 16)])
+@pytest.mark.parametrize("epilogue", ["none", "silu_gate"])
+def test_linear(K, xd, wd, od, n, o, k, epilogue):
+    x = rnd((n, k), xd, 4)
+    w = rnd((2 * o if epilogue == "silu_gate" else o, k), wd, 5, scale=k ** -0.5)
+    ref = torch.empty((n, o), dtype=od)
+    REF.linear(x, w, ref, epilogue)
+    out = torch.empty((n, o), dtype=od, device="cuda")
+    K.linear(x.cuda(), w.cuda(), out, epilogue)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(od))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rdim,inter,ps", [(4, 2, 16, 16, False, 16), (6, 3, 48, 48, False, 8),
+                                                    (5, 1, 80, 32, True, 5), (8, 8, 128, 128, False, 16)])
+def test_qk_norm_rope_store(K, dtype, nq, nkv, d, rdim, inter, ps):
+    n, pages = 23, 9
+    qkv = rnd((n, (nq + 2 * nkv) * d), dtype, 6)
+    qw = (1 + 0.1 * rnd((d,), torch.float32, 7)).to(dtype)
+    kw = (1 + 0.1 * rnd((d,), torch.float32, 8)).to(dtype)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, rdim, 2, dtype=torch.float32) / rdim))
+    positions = torch.randint(0, 5000, (n,), dtype=torch.int32)
+    slots = torch.randperm(pages * ps)[:n].to(torch.int32)
+    slots[3] = -1
+    kv_ref = torch.zeros((pages, 2, nkv, ps, d), dtype=dtype)
+    qkv_ref = qkv.clone()
+    ReferenceKernels(torch.float32).qk_norm_rope_store(qkv_ref, nq, nkv, d, qw, kw, 1e-6, inv_freq, rdim, inter,
+                                                       positions, slots, kv_ref)
+    kv_gpu, qkv_gpu = torch.zeros_like(kv_ref, device="cuda"), qkv.cuda()
+    K.qk_norm_rope_store(qkv_gpu, nq, nkv, d, qw.cuda(), kw.cuda(), 1e-6, inv_freq.cuda(), rdim, inter,
+                         positions.cuda(), slots.cuda(), kv_gpu)
+    t = dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=2e-2)
+    torch.testing.assert_close(qkv_gpu.cpu().float(), qkv_ref.float(), **t)
+    torch.testing.assert_close(kv_gpu.cpu().float(), kv_ref.float(), **t)
+    # what was not addressed stays zero
+    assert kv_gpu.cpu()[kv_ref == 0].abs().max() == 0
+    # no norm, no rotation: a pure store
+    kv2 = torch.zeros_like(kv_gpu)
+    before = qkv_gpu.clone()
+    K.qk_norm_rope_store(qkv_gpu, nq, nkv, d, None, None, 0.0, None, 0, False, positions.cuda(), slots.cuda(), kv2)
+    assert torch.equal(before, qkv_gpu) and torch.equal(kv2, kv_gpu)
+
+
+def _attention_case(dtype, nq, nkv, d, ps, window, q_lens, seq_lens, seed, spike=False):
+    g = torch.Generator().manual_seed(seed)
+    R = len(q_lens)
+    pages_per = [-(-L // ps) for L in seq_lens]
+    total_pages = sum(pages_per) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    P = max(pages_per) + 1
+    bt = torch.full((R, P), -1, dtype=torch.int32)
+    it = iter(perm)
+    for r in range(R):
+        for j in range(pages_per[r]):
+            bt[r, j] = next(it)
+    kv = (torch.randn((total_pages, 2, nkv, ps, d), generator=g)).to(dtype)
+    n = sum(q_lens)
+    qkv = torch.randn((n, (nq + 2 * nkv) * d), generator=g).to(dtype)
+    if spike:
+        # one far key of request 0 gets a score far above all others for the last query's first head
+        key_pos = 1
+        page, off = int(bt[0, key_pos // ps]), key_pos % ps
+        qrow = q_lens[0] - 1
+        q0 = qkv[qrow, :d].float()
+        kv[page, 0, 0, off] = (q0 / q0.norm() * 6.0 * math.sqrt(d) / q0.norm() * q0.norm()).to(dtype)
+        kv[page, 1, 0, off] = 7.0
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    if window:
+        # pages wholly below every query's window are stale: poison them
+        for r in range(R):
+            first = max(0, (seq_lens[r] - q_lens[r]) - window + 1) // ps
+            for j in range(first):
+                kv[int(bt[r, j])] = float("nan")
+                bt[r, j] = -1
+    return qkv, kv, bt, cu, sl
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,ps,window", [(4, 2, 16, 16, 0), (8, 2, 32, 8, 24), (6, 3, 48, 32, 40),
+                                                (16, 8, 128, 16, 0), (3, 1, 80, 5, 7), (2, 2, 256, 16, 0)])
+def test_paged_attention(K, dtype, nq, nkv, d, ps, window):
+    q_lens, seq_lens = [5, 1, 33, 1, 2], [5, 77, 100, 1, 130]
+    qkv, kv, bt, cu, sl = _attention_case(dtype, nq, nkv, d, ps, window, q_lens, seq_lens, 9, spike=(window == 0))
+    n = qkv.shape[0]
+    ref = torch.empty((n, nq * d), dtype=dtype)
+    REF.paged_attention(qkv, nq, nkv, d, kv, bt, cu, sl, ref, d ** -0.5, window, max(q_lens), max(seq_lens))
+    out = torch.empty((n, nq * d), dtype=dtype, device="cuda")
+    K.paged_attention(qkv.cuda(), nq, nkv, d, kv.cuda(), bt.cuda(), cu.cuda(), sl.cuda(), out, d ** -0.5, window,
+                      max(q_lens), max(seq_lens))
+    t = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **t)
+    if window == 0:
+        assert ref[q_lens[0] - 1, :d].float().mean() > 6.0     # the far key dominates where it was planted
+
+
+@pytest.mark.parametrize("vocab,rows", [(333, 3), (151936, 4), (1, 1), (5000, 7)])
+def test_sample(K, vocab, rows):
+    g = torch.Generator().manual_seed(10)
+    logits = torch.randn((rows, vocab), generator=g) * 3
+    if vocab > 10:
+        logits[0, 7] = logits[0, 3] = logits[0].max() + 1      # a tie: the lower index wins
+    temps = torch.tensor([0.0, 0.8, 1.5, 0.3, 0.0, 1.0, 0.05][:rows])
+    u = torch.rand((rows,), generator=g)
+    ref = torch.empty(rows, dtype=torch.int32)
+    REF.sample(logits, temps, u, ref)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    K.sample(logits.cuda(), temps.cuda(), u.cuda(), out)
+    out = out.cpu()
+    for m in range(rows):
+        if out[m] != ref[m]:
+            # float32 and float64 running sums may part only where u sits on a boundary
+            p = torch.softmax(logits[m].double() / float(temps[m]), -1).cumsum(0)
+            assert abs(int(out[m]) - int(ref[m])) == 1 and min(abs(p[int(out[m])] - u[m]), abs(p[int(ref[m])] - u[m])) < 1e-5
+    # greedy without temperature arrays
+    out2 = torch.empty(rows, dtype=torch.int32, device="cuda")
+    K.sample(logits.cuda(), None, None, out2)
+    assert torch.equal(out2.cpu().long(), logits.argmax(-1))
+    if vocab > 10:
+        assert int(out2[0]) == 3
+
+
+def test_refusals(K):
+    from infurnace_b200.errors import KernelError
+    with pytest.raises(KernelError):
+        K.paged_attention(torch.zeros((1, 3 * 512), device="cuda"), 1, 1, 512,
+                          torch.zeros((1, 2, 1, 16, 512), device="cuda"), torch.zeros((1, 1), dtype=torch.int32, device="cuda"),
+                          torch.tensor([0, 1], dtype=torch.int32, device="cuda"), torch.tensor([1], dtype=torch.int32, device="cuda"),
+                          torch.zeros((1, 512), device="cuda"), 1.0, 0, 1, 1)
+    with pytest.raises(KernelError):
+        K.linear(torch.zeros((2, 8), device="cuda"), torch.zeros((4, 9), device="cuda"), torch.zeros((2, 4), device="cuda"))
+    with pytest.raises(KernelError):
+        K.embed(torch.zeros((4, 8), device="cuda", dtype=torch.float16), torch.zeros(2, dtype=torch.int32, device="cuda"),
+                torch.zeros((2, 8), device="cuda"))
