@@ -129,12 +129,12 @@ def _attention_case(dtype, nq, nkv, d, ps, window, q_lens, seq_lens, seed, spike
     n = sum(q_lens)
     qkv = torch.randn((n, (nq + 2 * nkv) * d), generator=g).to(dtype)
     if spike:
-        # one far key of request 0 gets a score far above all others for the last query's first head
-        key_pos = 1
-        page, off = int(bt[0, key_pos // ps]), key_pos % ps
-        qrow = q_lens[0] - 1
-        q0 = qkv[qrow, :d].float()
-        kv[page, 0, 0, off] = (q0 / q0.norm() * 6.0 * math.sqrt(d) / q0.norm() * q0.norm()).to(dtype)
+        # a far key (position 1 of more than a hundred) of the last request gets a score far above
+        # all others for the last query's first head; its value row is all sevens
+        r = R - 1
+        page, off = int(bt[r, 1 // ps]), 1 % ps
+        q0 = qkv[n - 1, :d].float()
+        kv[page, 0, 0, off] = (q0 / q0.norm() * 6.0 * math.sqrt(d)).to(dtype)
         kv[page, 1, 0, off] = 7.0
     cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
     sl = torch.tensor(seq_lens, dtype=torch.int32)
@@ -163,7 +163,7 @@ def test_paged_attention(K, dtype, nq, nkv, d, ps, window):
     t = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
     torch.testing.assert_close(out.cpu().float(), ref.float(), **t)
     if window == 0:
-        assert ref[q_lens[0] - 1, :d].float().mean() > 6.0     # the far key dominates where it was planted
+        assert ref[n - 1, :d].float().mean() > 6.0     # the far key dominates where it was planted
 
 
 @pytest.mark.parametrize("vocab,rows", [(333, 3), (151936, 4), (1, 1), (5000, 7)])
