@@ -215,8 +215,9 @@ class Scheduler:
             budget -= self._plan_portion(req, budget, reserved, plan)
             planned.add(rid)
 
-        # 3. admit from the head of the queue
-        while self._waiting and budget >= 1 and len(self._running) < self.max_num_seqs \
+        # 3. admit from the head of the queue (not in a step that had to preempt: the pages a
+        #    victim gave back are for those that stayed)
+        while not plan.preempted and self._waiting and budget >= 1 and len(self._running) < self.max_num_seqs \
                 and self.cache.num_free_slots > 0:
             rid = self._waiting[0]
             req = self._requests[rid]

@@ -154,7 +154,7 @@ class ReferenceKernels:
         index); else the smallest index i with cumsum(softmax(logits/temperature))[i] >
         uniform[m] (the last index with non-zero probability if rounding leaves none)."""
         for m in range(logits.shape[0]):
-            t = float(temperature[m])
+            t = 0.0 if temperature is None else float(temperature[m])
             row = logits[m].double()
             if t == 0.0:
                 out[m] = int(torch.argmax(row))
