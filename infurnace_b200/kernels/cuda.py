@@ -57,6 +57,7 @@ class CudaKernels:
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device is available; this engine has no CPU path")
         self._progress = progress
+        self.launches = 0          # kernels launched through this object
         self.core = load_library("core", progress=progress)
         c = self.core
         c.ifb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
@@ -82,6 +83,7 @@ class CudaKernels:
         n, hidden = out.shape
         if table.shape[1] != hidden or ids.numel() != n:
             raise KernelError("embed: sizes of table, ids and out do not match")
+        self.launches += 1
         _check(self.core.ifb_embed(table.data_ptr(), _code(table), ids.data_ptr(), out.data_ptr(), n, hidden,
                                    self._stream()), "embed")
 
@@ -108,6 +110,7 @@ class CudaKernels:
                 raise KernelError("rmsnorm: out has a row for each entry of rows")
         elif n_out != x.shape[0]:
             raise KernelError("rmsnorm: out has a row for each row of x")
+        self.launches += 1
         _check(self.core.ifb_rmsnorm(x.data_ptr(), _ptr(delta), splits, stride, weight.data_ptr(), _code(weight),
                                      float(eps), out.data_ptr(), _code(out), _ptr(rows), n_out, hidden,
                                      self._stream()), "rmsnorm")
@@ -120,6 +123,7 @@ class CudaKernels:
         epi = {"none": 0, "silu_gate": 1}[epilogue]
         if w.shape[1] != k or out.shape[0] != n or w.shape[0] != (2 * o if epi else o):
             raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not match")
+        self.launches += 1
         _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
                                          n, o, k, epi, self._stream()), "linear")
 
@@ -150,6 +154,7 @@ class CudaKernels:
                     or kv_pages.shape[4] != head_dim or slot_mapping.numel() != n:
                 raise KernelError("qk_norm_rope_store: kv_pages is not [pages, 2, kv_heads, page_size, head_dim]")
             page_size = kv_pages.shape[3]
+        self.launches += 1
         _check(self.core.ifb_qk_norm_rope_store(
             qkv.data_ptr(), _code(qkv), n, num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight), wd,
             float(eps), _ptr(inv_freq), int(rotary_dim), int(bool(interleaved)), _ptr(positions), _ptr(slot_mapping),
@@ -169,6 +174,7 @@ class CudaKernels:
         if kv_pages.dim() != 5 or kv_pages.shape[1] != 2 or kv_pages.shape[2] != num_kv_heads \
                 or kv_pages.shape[4] != head_dim:
             raise KernelError("paged_attention: kv_pages is not [pages, 2, kv_heads, page_size, head_dim]")
+        self.launches += 1
         _check(self.core.ifb_paged_attention_simt(
             qkv.data_ptr(), _code(qkv), qkv.stride(0), kv_pages.data_ptr(), block_tables.data_ptr(),
             block_tables.stride(0), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), n, r, num_heads,
@@ -184,5 +190,6 @@ class CudaKernels:
                 raise KernelError("sample: one temperature and one uniform number per row")
         if out.numel() != m:
             raise KernelError("sample: out has one entry per row")
+        self.launches += 1
         _check(self.core.ifb_sample(logits.data_ptr(), m, vocab, _ptr(temperature), _ptr(uniform), out.data_ptr(),
                                     self._stream()), "sample")
