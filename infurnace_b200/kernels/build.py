@@ -30,10 +30,17 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"
 # library name -> (sources, extra flags)
 LIBRARIES: Dict[str, tuple] = {
     "core": (["elementwise.cu", "linear_simt.cu", "attention_simt.cu"], []),
+    # compiled once per head size: defines={"HEAD_DIM": d}
+    "attention_mma": (["attention_mma.cu"], []),
 }
+
+# what the build check compiles beside "core": the head size of the Qwen3 checkpoints and those of
+# the tiny test models; any other multiple of 16 up to 256 is compiled when a model first needs it
+DEFAULT_VARIANTS = [("attention_mma", {"HEAD_DIM": d}) for d in (128, 16, 32, 48)]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 def _say(progress, msg):
@@ -51,19 +58,24 @@ def find_nvcc() -> str:
     raise KernelError("nvcc was not found (PATH, CUDA_HOME, /usr/local/cuda): the CUDA kernels cannot be compiled")
 
 
+_build_dir: Optional[str] = None
+
+
 def build_dir() -> str:
-    d = os.path.join(os.path.dirname(CSRC), "_build")
-    try:
-        os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return d
-    except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"infurnace_b200-build-{os.getuid()}")
-        os.makedirs(d, exist_ok=True)
-        return d
+    global _build_dir
+    with _dir_lock:
+        if _build_dir is None:
+            d = os.path.join(os.path.dirname(CSRC), "_build")
+            try:
+                os.makedirs(d, exist_ok=True)
+                fd, probe = tempfile.mkstemp(dir=d)
+                os.close(fd)
+                os.remove(probe)
+            except OSError:
+                d = os.path.join(tempfile.gettempdir(), f"infurnace_b200-build-{os.getuid()}")
+                os.makedirs(d, exist_ok=True)
+            _build_dir = d
+        return _build_dir
 
 
 def _hash(sources: Sequence[str], flags: Sequence[str]) -> str:
@@ -134,4 +146,7 @@ def load_library(name: str, defines: Optional[Dict[str, object]] = None, progres
 
 def build_all(progress=None) -> List[str]:
     """Compile every library (used by the build check; needs no GPU)."""
-    return [compile_library(name, None, progress) for name in LIBRARIES]
+    from concurrent.futures import ThreadPoolExecutor
+    jobs = [("core", None)] + DEFAULT_VARIANTS
+    with ThreadPoolExecutor(max_workers=4) as pool:
+        return list(pool.map(lambda j: compile_library(j[0], j[1], progress), jobs))

@@ -69,6 +69,10 @@ class CudaKernels:
         c.ifb_sample.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
         c.ifb_linear_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_void_p]
+        self._attn_mma = {}        # head size -> library
+        self._attn_scratch = None
+        self.sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        self.attention_scratch_cap = 64 << 20     # bytes of split scratch beyond which a step runs unsplit
         c.ifb_paged_attention_simt.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                                c_void_p]
@@ -174,11 +178,58 @@ class CudaKernels:
         if kv_pages.dim() != 5 or kv_pages.shape[1] != 2 or kv_pages.shape[2] != num_kv_heads \
                 or kv_pages.shape[4] != head_dim:
             raise KernelError("paged_attention: kv_pages is not [pages, 2, kv_heads, page_size, head_dim]")
+        group = num_heads // num_kv_heads
+        if qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and group <= 16 \
+                and num_heads % num_kv_heads == 0:
+            return self._paged_attention_mma(qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q,
+                                             seq_lens, out, scale, window, max_q_len, max_seq_len, n, r)
         self.launches += 1
         _check(self.core.ifb_paged_attention_simt(
             qkv.data_ptr(), _code(qkv), qkv.stride(0), kv_pages.data_ptr(), block_tables.data_ptr(),
             block_tables.stride(0), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), n, r, num_heads,
             num_kv_heads, head_dim, kv_pages.shape[3], float(scale), int(window), self._stream()), "paged_attention")
+
+    def attention_library(self, head_dim):
+        lib = self._attn_mma.get(head_dim)
+        if lib is None:
+            lib = load_library("attention_mma", {"HEAD_DIM": head_dim}, progress=self._progress)
+            lib.ifb_attention_mma.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                              c_int, c_int, c_int, c_void_p]
+            lib.ifb_attention_mma_scratch_floats.restype = c_longlong
+            lib.ifb_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int]
+            self._attn_mma[head_dim] = lib
+        return lib
+
+    def attention_splits(self, num_requests, num_kv_heads, max_seq_len, window=0):
+        """How many CTAs share one (request, key/value head) of the small-q kernel: enough to
+        give every SM two CTAs, and no fewer than 256 keys per split."""
+        reach = min(max_seq_len, window + 16) if window else max_seq_len
+        want = -(-2 * self.sm_count // max(1, num_requests * num_kv_heads))
+        return max(1, min(want, -(-reach // 256), 32))
+
+    def attention_scratch(self, floats):
+        if self._attn_scratch is None or self._attn_scratch.numel() < floats:
+            self._attn_scratch = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device="cuda")
+        return self._attn_scratch
+
+    def _paged_attention_mma(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out,
+                             scale, window, max_q_len, max_seq_len, n, r, num_splits=None):
+        lib = self.attention_library(head_dim)
+        group = num_heads // num_kv_heads
+        only_small = max_q_len * group <= 16
+        if num_splits is None:
+            num_splits = self.attention_splits(r, num_kv_heads, max_seq_len, window)
+        need = lib.ifb_attention_mma_scratch_floats(n, num_heads, num_splits)
+        if need * 4 > self.attention_scratch_cap:
+            num_splits, need = 1, 0
+        scratch = self.attention_scratch(need) if need else None
+        self.launches += (2 if num_splits > 1 else 1) + (0 if only_small else 1)
+        _check(lib.ifb_attention_mma(
+            qkv.data_ptr(), qkv.stride(0), kv_pages.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+            cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), _ptr(scratch), n, r, num_heads, num_kv_heads,
+            head_dim, kv_pages.shape[3], float(scale), int(window), int(max_q_len), int(num_splits), 1,
+            0 if only_small else 1, self._stream()), "paged_attention")
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):

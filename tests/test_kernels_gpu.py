@@ -204,3 +204,22 @@ def test_refusals(K):
     with pytest.raises(KernelError):
         K.embed(torch.zeros((4, 8), device="cuda", dtype=torch.float16), torch.zeros(2, dtype=torch.int32, device="cuda"),
                 torch.zeros((2, 8), device="cuda"))
+
+
+@pytest.mark.parametrize("nq,nkv,d,ps,window,splits", [(16, 8, 128, 16, 0, 5), (8, 2, 32, 8, 0, 3), (6, 3, 48, 32, 100, 4),
+                                                       (4, 4, 64, 16, 0, 32), (16, 1, 16, 64, 0, 2)])
+def test_attention_split_over_the_context(K, nq, nkv, d, ps, window, splits):
+    """Decoded tokens and two-token portions with the context split over several CTAs (more
+    splits than some requests have tiles), merged by the second kernel; prompts beside them."""
+    dtype = torch.bfloat16
+    g = nq // nkv
+    small = max(1, 16 // g)
+    q_lens, seq_lens = [1, min(2, small), 1, 40, 1], [700, 1000, 3, 300, 65]
+    qkv, kv, bt, cu, sl = _attention_case(dtype, nq, nkv, d, ps, window, q_lens, seq_lens, 12, spike=(window == 0))
+    n = qkv.shape[0]
+    ref = torch.empty((n, nq * d), dtype=dtype)
+    REF.paged_attention(qkv, nq, nkv, d, kv, bt, cu, sl, ref, d ** -0.5, window, max(q_lens), max(seq_lens))
+    out = torch.full((n, nq * d), float("nan"), dtype=dtype, device="cuda")
+    K._paged_attention_mma(qkv.cuda(), nq, nkv, d, kv.cuda(), bt.cuda(), cu.cuda(), sl.cuda(), out, d ** -0.5, window,
+                           max(q_lens), max(seq_lens), n, len(q_lens), num_splits=splits)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2, atol=1.6e-2)
