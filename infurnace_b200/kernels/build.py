@@ -29,7 +29,7 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"
 
 # library name -> (sources, extra flags)
 LIBRARIES: Dict[str, tuple] = {
-    "core": (["elementwise.cu", "linear_simt.cu", "attention_simt.cu"], []),
+    "core": (["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "linear_skinny.cu"], []),
     # compiled once per head size: defines={"HEAD_DIM": d}
     "attention_mma": (["attention_mma.cu"], []),
 }

@@ -69,6 +69,13 @@ class CudaKernels:
         c.ifb_sample.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
         c.ifb_linear_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_void_p]
+        c.ifb_linear_skinny.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                        c_int, c_int, c_void_p]
+        c.ifb_linear_skinny_scratch.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+        c.ifb_linear_skinny_scratch.restype = None
+        self._lin_partials = None
+        self._lin_counters = None
+        self.skinny_max_rows = 4096    # above this the plain kernel runs (until a large-tile kernel takes over)
         self._attn_mma = {}        # head size -> library
         self._attn_scratch = None
         self.sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
@@ -127,9 +134,35 @@ class CudaKernels:
         epi = {"none": 0, "silu_gate": 1}[epilogue]
         if w.shape[1] != k or out.shape[0] != n or w.shape[0] != (2 * o if epi else o):
             raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not match")
+        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 and n <= self.skinny_max_rows \
+                and out.dtype in (torch.bfloat16, torch.float32):
+            return self._linear_skinny(x, w, out, n, o, k, epi)
         self.launches += 1
         _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
                                          n, o, k, epi, self._stream()), "linear")
+
+    def linear_splits(self, n, o, k):
+        """CTAs that share the k range of one 64-feature tile: enough to cover the SMs twice, and
+        at least 256 of k each."""
+        blocks = 1 if n <= 8 else 2 if n <= 16 else 4 if n <= 32 else 8
+        tiles = -(-o // 64) * -(-n // (blocks * 8))
+        return max(1, min(-(-2 * self.sm_count // tiles), k // 256))
+
+    def _linear_skinny(self, x, w, out, n, o, k, epi, splits=None):
+        if splits is None:
+            splits = self.linear_splits(n, o, k)
+        partials = counters = None
+        if splits > 1:
+            nf, nc = ctypes.c_longlong(), ctypes.c_longlong()
+            self.core.ifb_linear_skinny_scratch(n, o, epi, splits, ctypes.byref(nf), ctypes.byref(nc))
+            if self._lin_partials is None or self._lin_partials.numel() < nf.value:
+                self._lin_partials = torch.empty(max(nf.value, 1 << 20), dtype=torch.float32, device="cuda")
+            if self._lin_counters is None or self._lin_counters.numel() < nc.value:
+                self._lin_counters = torch.zeros(max(nc.value, 1 << 14), dtype=torch.int32, device="cuda")
+            partials, counters = self._lin_partials, self._lin_counters
+        self.launches += 1
+        _check(self.core.ifb_linear_skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), _ptr(partials),
+                                           _ptr(counters), n, o, k, epi, splits, self._stream()), "linear")
 
     # ------------------------------------------------------------------ q/k norm, rotation, store
     def qk_norm_rope_store(self, qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, inv_freq,

@@ -223,3 +223,25 @@ def test_attention_split_over_the_context(K, nq, nkv, d, ps, window, splits):
     K._paged_attention_mma(qkv.cuda(), nq, nkv, d, kv.cuda(), bt.cuda(), cu.cuda(), sl.cuda(), out, d ** -0.5, window,
                            max(q_lens), max(seq_lens), n, len(q_lens), num_splits=splits)
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2, atol=1.6e-2)
+
+
+@pytest.mark.parametrize("od", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,o,k,splits", [(1, 72, 72, 1), (8, 4096, 1024, 2), (3, 1000, 3072, 7), (16, 333, 136, 1),
+                                          (17, 64, 1024, 4), (64, 1024, 2048, 5), (33, 200, 1000, 3), (100, 130, 520, 2),
+                                          (1, 151936, 1024, 1)])
+@pytest.mark.parametrize("epilogue", ["none", "silu_gate"])
+def test_linear_skinny(K, od, n, o, k, splits, epilogue):
+    """The few-rows tensor-core product, with k split over several CTAs and merged by the last one;
+    twice in a row, so that the counters it leaves behind are shown to be clean."""
+    if o > 100000 and epilogue != "none":
+        pytest.skip("one large case is enough")
+    x = rnd((n, k), torch.bfloat16, 4)
+    w = rnd((2 * o if epilogue == "silu_gate" else o, k), torch.bfloat16, 5, scale=k ** -0.5)
+    ref = torch.empty((n, o), dtype=od)
+    REF.linear(x, w, ref, epilogue)
+    xg, wg = x.cuda(), w.cuda()
+    for _ in range(2):
+        out = torch.full((n, o), float("nan"), dtype=od, device="cuda")
+        K._linear_skinny(xg, wg, out, n, o, k, 1 if epilogue == "silu_gate" else 0, splits=splits)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2 if od == torch.bfloat16 else 2e-4,
+                                   atol=2e-3 if od == torch.bfloat16 else 1e-4)
