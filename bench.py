@@ -169,23 +169,28 @@ def time_decode(runner, sampler, rids, vocab, steps, warmup, seed=1):
     from infurnace_b200.engine.runner import StepEntry
     g = torch.Generator().manual_seed(seed)
     ids = torch.randint(0, vocab, (warmup + steps, len(rids)), generator=g).tolist()
-    out = torch.empty(len(rids), dtype=torch.int32, device="cuda")
+    zeros = [0.0] * len(rids)
 
     def one(k):
-        logits = runner.step([StepEntry(rid, [ids[k][j]], [0]) for j, rid in enumerate(rids)])
-        runner.rt.kernels.sample(logits, None, None, out)
+        # the step function with the sampling kernel behind it; decode-only steps replay a CUDA graph
+        runner.step_and_sample([StepEntry(rid, [ids[k][j]], [0]) for j, rid in enumerate(rids)], zeros, zeros)
 
     for k in range(warmup):
         one(k)
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = runner.rt.kernels.launches
+    replays0 = runner.graph_replays
     start.record()
     for k in range(warmup, warmup + steps):
         one(k)
     end.record()
     torch.cuda.synchronize()
-    return start.elapsed_time(end), runner.rt.kernels.launches - launches0
+    launches = runner.rt.kernels.launches - launches0
+    replays = runner.graph_replays - replays0
+    if replays:          # a replayed step launches what one recorded step launched
+        launches += replays * runner.launches_per_graph_step
+    return start.elapsed_time(end), launches
 
 
 def run_ours(args):
@@ -201,7 +206,7 @@ def run_ours(args):
     batch, steps, warmup = args.batch, args.steps, args.warmup
     layers_full = cfg.num_hidden_layers
     page = 16
-    big = 64                                           # the largest batch of the run
+    big = 64 if args.mode == "all" else batch          # the largest batch of the run
     pool_tokens = big * CONTEXT + PREFILL_TOKENS + 64
     with tempfile.TemporaryDirectory(prefix="infurnace_b200_bench_") as d:
         write_random_model(cfg, 0, d)
@@ -209,6 +214,17 @@ def run_ours(args):
                              max_num_batched_tokens=PREFILL_TOKENS, max_model_len=CONTEXT)
         engine = Engine.from_model_dir(d, opts)
     runner, plan = engine.runner, engine.plan
+    if args.eager:
+        runner.use_graphs = False
+    if args.mode == "prefill":
+        toks = torch.randint(0, cfg.vocab_size, (PREFILL_TOKENS,)).tolist()
+        for rep in range(max(1, steps)):
+            runner.cache.add_request("p")
+            runner.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])])
+            torch.cuda.synchronize()
+            runner.cache.free_request("p")
+        print(json.dumps({"mode": "prefill", "tokens": PREFILL_TOKENS, "steps": max(1, steps)}))
+        return 0
     sampler = Sampler(runner.rt.kernels, runner.rt.device)
     randomize_pages(runner)
     torch.cuda.synchronize()
@@ -223,6 +239,10 @@ def run_ours(args):
     release(runner, rids)
     ms_per_step = ms / steps
     value = batch * steps / (ms / 1000.0)
+    if args.mode == "decode":
+        print(json.dumps({"mode": "decode", "batch": batch, "context": CONTEXT, "steps": steps, "ms_per_step": ms_per_step,
+                          "tokens_per_s": value, "graphs": runner.use_graphs, "launches": launches}))
+        return 0
     mean_ctx = CONTEXT - steps / 2
     w_bytes, kv_bytes = decode_bytes(plan, runner, [mean_ctx] * batch, 2)
     achieved = (w_bytes + kv_bytes) / (ms_per_step / 1000.0) / 1e9
@@ -324,6 +344,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--mode", default="all", choices=("all", "decode", "prefill"),
+                    help="decode / prefill: only that part, on a pool just large enough (for profiling a small case)")
+    ap.add_argument("--eager", action="store_true", help="launch every kernel of a decode step instead of replaying a graph")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -33,6 +33,7 @@ constexpr int BN = 64;             // keys per tile
 constexpr int THREADS = 128;
 constexpr int KCH = D / 8;         // 16-byte pieces of a row
 constexpr int KB = D / 16;         // k-blocks of a q.k product, n-block pairs of a p.v product
+constexpr int SQ_STAGES = 3;       // tile buffers of the small-q kernel: two tiles are in flight while one is used
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -60,18 +61,27 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Keys key0 .. key0+BN-1 of one key/value head into Ks and Vs ([BN][DP]); keys outside [lo, hi] are zeros.
+// Consecutive threads copy consecutive 16-byte pieces of a row, so a warp's copy instruction covers whole
+// 128-byte lines (a piece per thread at scattered rows would cost a memory request each).
 __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ pages,
                                              const int* __restrict__ bt, int key0, int lo, int hi, int kvh, int nkv,
                                              int page_size, int tid) {
   const size_t head_stride = (size_t)page_size * D, page_stride = 2 * (size_t)nkv * head_stride;
-  for (int c = tid; c < BN * KCH; c += THREADS) {
+  const int ps_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;   // power of two: shift, else divide
+  constexpr int PASSES = (BN * KCH + THREADS - 1) / THREADS;
+#pragma unroll
+  for (int ps = 0; ps < PASSES; ++ps) {
+    const int c = tid + ps * THREADS;
+    if ((BN * KCH) % THREADS != 0 && c >= BN * KCH) break;
     const int row = c / KCH, ch = c % KCH;
     const int key = key0 + row;
     const bool valid = key >= lo && key <= hi;
     const bf16* src = pages;
     if (valid) {
-      const int page = bt[key / page_size];
-      src = pages + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)(key % page_size) * D + ch * 8;
+      int pi, off;
+      if (ps_shift >= 0) { pi = key >> ps_shift; off = key & (page_size - 1); }
+      else { pi = key / page_size; off = key - pi * page_size; }
+      src = pages + (size_t)bt[pi] * page_stride + (size_t)kvh * head_stride + (size_t)off * D + ch * 8;
     }
     cp_async16(Ks + row * DP + ch * 8, src, valid);
     cp_async16(Vs + row * DP + ch * 8, valid ? src + (size_t)nkv * head_stride : pages, valid);
@@ -81,7 +91,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
 // One warp: scores of its 16 query rows (fragments qf) against keys [kbeg, kbeg + 8*NB) of the tile in
 // Ks/Vs, masking, online softmax update of (m, l, o).  Row A of a thread is lane/4, row B is that + 8.
 // pA/pB: position of the row's query (-1000000000: the row does not exist); wlo: window (0: none).
-template <int NB>
+template <int NB, bool MASK>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KB][4], const bf16* Ks, const bf16* Vs, int kbeg,
                                           int key0, int klo, int khi, int pA, int pB, int window, float scale_log2,
                                           float (&m)[2], float (&l)[2], float (&o)[D / 8][4], int lane) {
@@ -107,9 +117,13 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KB][4], const bf1
   for (int j = 0; j < NB; ++j) {
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      const int key = key0 + kbeg + j * 8 + ((lane & 3) << 1) + e;
-      const bool in = key >= klo && key <= khi;
-      const bool va = in && key <= pA && key >= loA, vb = in && key <= pB && key >= loB;
+      bool va = true, vb = true;
+      if (MASK) {
+        const int key = key0 + kbeg + j * 8 + ((lane & 3) << 1) + e;
+        const bool in = key >= klo && key <= khi;
+        va = in && key <= pA && key >= loA;
+        vb = in && key <= pB && key >= loB;
+      }
       s[j][e] = va ? s[j][e] * scale_log2 : -INFINITY;
       s[j][2 + e] = vb ? s[j][2 + e] * scale_log2 : -INFINITY;
       mxA = fmaxf(mxA, s[j][e]);
@@ -181,7 +195,7 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
                     int num_splits) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][DP]
-  bf16* KV = Qs + 16 * DP;                                   // 2 stages x (K [BN][DP], V [BN][DP])
+  bf16* KV = Qs + 16 * DP;                                   // SQ_STAGES x (K [BN][DP], V [BN][DP])
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = nq / nkv;
@@ -204,8 +218,15 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
     const bf16* src = valid ? qkv + (size_t)(q0 + row / G) * row_stride + (size_t)(kvh * G + row % G) * D + ch * 8 : qkv;
     cp_async16(Qs + row * DP + ch * 8, src, valid);
   }
-  if (n_tiles > 0) load_kv_tile(KV, KV + BN * DP, pages, bt, k_begin, k_begin, k_end - 1, kvh, nkv, page_size, tid);
-  cp_async_commit();
+  // prologue: tiles 0 .. SQ_STAGES-2 in flight (one commit group per tile, empty groups past the end)
+#pragma unroll
+  for (int st = 0; st < SQ_STAGES - 1; ++st) {
+    if (st < n_tiles) {
+      bf16* Kn = KV + st * 2 * BN * DP;
+      load_kv_tile(Kn, Kn + BN * DP, pages, bt, k_begin + st * BN, k_begin, k_end - 1, kvh, nkv, page_size, tid);
+    }
+    cp_async_commit();
+  }
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[D / 8][4];
@@ -215,20 +236,26 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
   const int pA = rowA < rows ? p_first + rowA / G : NO_ROW, pB = rowB < rows ? p_first + rowB / G : NO_ROW;
   uint32_t qf[KB][4];
   for (int t = 0; t < n_tiles; ++t) {
-    bf16* Ks = KV + (t & 1) * 2 * BN * DP;
+    const int stage = t % SQ_STAGES;
+    bf16* Ks = KV + stage * 2 * BN * DP;
     bf16* Vs = Ks + BN * DP;
-    if (t + 1 < n_tiles) {
-      bf16* Kn = KV + ((t + 1) & 1) * 2 * BN * DP;
-      load_kv_tile(Kn, Kn + BN * DP, pages, bt, k_begin + (t + 1) * BN, k_begin, k_end - 1, kvh, nkv, page_size, tid);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    cp_async_wait<SQ_STAGES - 2>();          // tile t has landed (for this thread's copies)
+    __syncthreads();                         // ... for everyone's; and everyone is done with tile t-1
+    const int nt = t + SQ_STAGES - 1;        // refill the stage that tile t-1 used
+    if (nt < n_tiles) {
+      bf16* Kn = KV + (nt % SQ_STAGES) * 2 * BN * DP;
+      load_kv_tile(Kn, Kn + BN * DP, pages, bt, k_begin + nt * BN, k_begin, k_end - 1, kvh, nkv, page_size, tid);
     }
-    __syncthreads();
+    cp_async_commit();
     if (t == 0) load_q_frags(qf, Qs, lane);
-    warp_tile<2>(qf, Ks, Vs, warp * 16, k_begin + t * BN, k_begin, k_end - 1, pA, pB, window, scale_log2, m, l, o, lane);
-    __syncthreads();
+    // a tile every key of which every existing row sees needs no masking (rows that do not exist have
+    // zero queries and are never written)
+    const int tile0 = k_begin + t * BN;
+    const bool interior = tile0 + BN - 1 <= min(p_first, k_end - 1) && (window == 0 || tile0 >= L - window);
+    if (interior)
+      warp_tile<2, false>(qf, Ks, Vs, warp * 16, tile0, k_begin, k_end - 1, pA, pB, window, scale_log2, m, l, o, lane);
+    else
+      warp_tile<2, true>(qf, Ks, Vs, warp * 16, tile0, k_begin, k_end - 1, pA, pB, window, scale_log2, m, l, o, lane);
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -359,8 +386,16 @@ attn_tile_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __res
     }
     __syncthreads();
     if (t == 0) load_q_frags(qf, Qs + warp * 16 * DP, lane);
-    if (lo + t * BN <= warp_hi)
-      warp_tile<8>(qf, Ks, Vs, 0, lo + t * BN, lo, hi, pA, pB, window, scale_log2, m, l, o, lane);
+    const int tile0 = lo + t * BN;
+    if (tile0 <= warp_hi) {
+      // every key of the tile is seen by every row of this warp: no masking
+      const bool interior = t0 + warp * tpw < t1 && tile0 >= lo && tile0 + BN - 1 <= min(hi, p_first + t0 + warp * tpw) &&
+                            (window == 0 || tile0 >= warp_hi - window + 1);
+      if (interior)
+        warp_tile<8, false>(qf, Ks, Vs, 0, tile0, lo, hi, pA, pB, window, scale_log2, m, l, o, lane);
+      else
+        warp_tile<8, true>(qf, Ks, Vs, 0, tile0, lo, hi, pA, pB, window, scale_log2, m, l, o, lane);
+    }
     __syncthreads();
   }
 #pragma unroll
@@ -383,7 +418,7 @@ attn_tile_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __res
   }
 }
 
-static size_t small_q_smem() { return (size_t)(16 * DP + 4 * BN * DP) * sizeof(bf16); }
+static size_t small_q_smem() { return (size_t)(16 * DP + SQ_STAGES * 2 * BN * DP) * sizeof(bf16); }
 static size_t tile_smem() { return (size_t)(64 * DP + 4 * BN * DP) * sizeof(bf16); }
 
 IFB_EXPORT int ifb_attention_mma_head_dim() { return D; }

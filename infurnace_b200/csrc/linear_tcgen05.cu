@@ -1,0 +1,298 @@
+// Matrix product for many rows (prompts): out[n, o] = sum_k x[n, k] w[o, k], bfloat16 operands,
+// float32 accumulation, on the fifth-generation tensor cores: tcgen05.mma issued by one thread, operands
+// brought to shared memory by TMA (128-byte swizzle), the accumulator in tensor memory, read back with
+// tcgen05.ld for the epilogue.
+//
+// One CTA per 128 x 128 output tile (tokens x features), 192 threads:
+//   warp 0, one thread: TMA producer.  Per 64-wide k block it waits for a free stage, arms the stage's
+//           "full" barrier with the byte count and issues the loads of the x tile and the w tile(s).
+//   warp 1, one thread: MMA issuer.  It waits for "full", issues four k=16 MMAs per tile and commits them
+//           to the stage's "empty" barrier, so the stage is reused as soon as the tensor core has read it.
+//           After the last k block it commits to the "accumulator ready" barrier.  Warp 1 also owns the
+//           allocation of tensor memory.
+//   warps 2-5: epilogue.  Each reads its quarter of the accumulator's 128 lanes (one token per thread),
+//           applies the epilogue and stores the row piece.
+// Rows, features or k beyond the matrices are zero-filled by TMA and dropped at the store.
+//
+// Epilogue 1 (silu_gate): w holds gate rows [0, O) and up rows [O, 2O); a stage carries both w tiles, the
+// accumulator has two halves of 128 columns, and out = silu(gate) * up.
+//
+// Every wait on a barrier is bounded: after G_SPIN_LIMIT polls the thread writes a code to `*err`, raises
+// the CTA's abort flag, and everything falls through to the common exit, which frees the tensor memory.
+#include "common.cuh"
+#include <cuda.h>
+
+typedef __nv_bfloat16 bf16;
+constexpr int G_BM = 128;          // tokens per tile  (MMA M)
+constexpr int G_BN = 128;          // features per tile (MMA N)
+constexpr int G_BK = 64;           // k per stage: 128 bytes, one swizzle row
+constexpr int G_UK = 16;           // k per MMA
+constexpr int G_THREADS = 192;
+constexpr uint32_t G_SPIN_LIMIT = 1u << 22;
+constexpr int G_TILE_BYTES = G_BM * G_BK * 2;   // 16 KB, same for an x tile and a w tile
+
+template <int EPI> struct GemmCfg {
+  static constexpr int NB = EPI ? 2 : 1;                      // w tiles per stage
+  static constexpr int STAGES = EPI ? 4 : 3;                  // 4 x 48 KB, or 3 x 32 KB (two CTAs per SM)
+  static constexpr int STAGE_BYTES = (1 + NB) * G_TILE_BYTES;
+  static constexpr int TMEM_COLS = NB * G_BN;                 // 128 or 256 columns of 32 bits
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+__device__ __forceinline__ uint32_t g_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(g_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(g_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(g_smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  False: gave up (the abort flag is up and *err says where).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+  for (uint32_t i = 0; i < G_SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(err, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(g_smem_u32(smem)), "l"(map), "r"(g_smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, int cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(g_smem_u32(slot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, int cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(g_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128 bytes, groups of 8
+// rows 1024 bytes apart (stride byte offset), leading byte offset unused (1), descriptor version 1.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: float32 accumulator, bfloat16 a and b, both K-major, N = 128, M = 128.
+constexpr uint32_t G_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(G_BN >> 3) << 17) | ((uint32_t)(G_BM >> 4) << 24);
+
+template <int EPI, typename TO>
+__global__ void __launch_bounds__(G_THREADS)
+linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                      TO* __restrict__ out, int n_rows, int o_out, int k_dim, int* __restrict__ err) {
+  using Cfg = GemmCfg<EPI>;
+  extern __shared__ unsigned char g_smem_raw[];
+  const uint32_t raw = g_smem_u32(g_smem_raw);
+  unsigned char* smem = g_smem_raw + (((raw + 1023u) & ~1023u) - raw);      // tiles need 1024-byte alignment
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty = full + Cfg::STAGES;
+  uint64_t* accum = empty + Cfg::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * G_BM, n0 = blockIdx.x * G_BN;
+  const int kblocks = (k_dim + G_BK - 1) / G_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(accum, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < kblocks; ++kb) {
+        const int s = kb % Cfg::STAGES;
+        const uint32_t ph = (kb / Cfg::STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, err, 1)) break;
+        unsigned char* stage = smem + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+        tma_load_2d(stage, &tmap_x, &full[s], kb * G_BK, m0);
+        tma_load_2d(stage + G_TILE_BYTES, &tmap_w, &full[s], kb * G_BK, n0);
+        if (EPI) tma_load_2d(stage + 2 * G_TILE_BYTES, &tmap_w, &full[s], kb * G_BK, o_out + n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < kblocks && ok; ++kb) {
+        const int s = kb % Cfg::STAGES;
+        const uint32_t ph = (kb / Cfg::STAGES) & 1;
+        ok = mbar_wait(&full[s], ph, abort_flag, err, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = g_smem_u32(smem + s * Cfg::STAGE_BYTES);
+        const uint64_t a_desc = make_smem_desc(a_addr);
+        const uint64_t b_desc = make_smem_desc(a_addr + G_TILE_BYTES);
+        const uint64_t b2_desc = make_smem_desc(a_addr + 2 * G_TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < G_BK / G_UK; ++k) {
+          const uint64_t step = (uint64_t)((k * G_UK * 2) >> 4);          // 32 bytes per k step, in 16-byte units
+          const uint32_t acc = (kb | k) != 0;
+          umma_bf16(tmem_base, a_desc + step, b_desc + step, G_IDESC, acc);
+          if (EPI) umma_bf16(tmem_base + G_BN, a_desc + step, b2_desc + step, G_IDESC, acc);
+        }
+        umma_commit(&empty[s]);
+      }
+      if (ok) umma_commit(accum);
+    }
+  } else {
+    const int q = warp & 3;                                      // this warp's quarter of the 128 lanes
+    const int row = m0 + q * 32 + lane;
+    if (mbar_wait(accum, 0, abort_flag, err, 3)) {
+      tc_fence_after();
+      const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+      const bool vec = ((size_t)o_out * sizeof(TO)) % 16 == 0 && (((uintptr_t)out) & 15) == 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < G_BN; c0 += 32) {
+        uint32_t v[32];
+        float y[32];
+        tmem_ld32(lane_base + c0, v);
+        if (EPI) {
+          uint32_t u[32];
+          tmem_ld32(lane_base + G_BN + c0, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float g = __uint_as_float(v[j]);
+            y[j] = g / (1.f + expf(-g)) * __uint_as_float(u[j]);
+          }
+        } else {
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
+        }
+        if (row < n_rows) {
+          TO* dst = out + (size_t)row * o_out + n0 + c0;
+          if (vec && n0 + c0 + 32 <= o_out) {
+            if (sizeof(TO) == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(y[j], y[j + 1]), p1 = __floats2bfloat162_rn(y[j + 2], y[j + 3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(y[j + 4], y[j + 5]), p3 = __floats2bfloat162_rn(y[j + 6], y[j + 7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&p0); pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                pk.z = *reinterpret_cast<uint32_t*>(&p2); pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + j) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c0 + j < o_out) dst[j] = from_f32<TO>(y[j]);
+          }
+        }
+      }
+    }
+  }
+  if (*abort_flag) {                         // a wait gave up: let copies in flight land before the CTA goes away
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, Cfg::TMEM_COLS); }
+}
+
+// ---------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, k] bfloat16 row-major matrix as a tensor map with boxes of 64 k x box_rows rows, 128-byte swizzle.
+static int make_map(CUtensorMap* m, const void* ptr, int rows, int k, int box_rows) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return IFB_ERR_ARG;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  cuuint32_t box[2] = {(cuuint32_t)G_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? IFB_OK : IFB_ERR_ARG;
+}
+
+template <int EPI, typename TO>
+static int tc_launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int n, int o, int k, int* err, cudaStream_t s) {
+  using Cfg = GemmCfg<EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_kernel<EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return -(int)e;
+    configured = true;
+  }
+  dim3 grid((o + G_BN - 1) / G_BN, (n + G_BM - 1) / G_BM);
+  linear_tcgen05_kernel<EPI, TO><<<grid, G_THREADS, Cfg::SMEM_BYTES, s>>>(mx, mw, (TO*)out, n, o, k, err);
+  return ifb_launch_status();
+}
+
+// x [n_rows, k] and w [out_features (x2 for the silu_gate epilogue), k] bfloat16, 16-byte aligned, k a multiple of 8;
+// out bfloat16 or float32.  `err` points to a device int that stays 0 unless a bounded wait gave up.
+IFB_EXPORT int ifb_linear_tcgen05(const void* x, const void* w, void* out, int out_dtype, int n_rows, int out_features,
+                                  int k_dim, int epilogue, int* err, cudaStream_t stream) {
+  if (n_rows <= 0 || out_features <= 0) return IFB_OK;
+  if (k_dim < 8 || k_dim % 8) return IFB_ERR_SIZE;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return IFB_ERR_ALIGN;
+  if (epilogue != 0 && epilogue != 1) return IFB_ERR_ARG;
+  if ((n_rows + G_BM - 1) / G_BM > 65535) return IFB_ERR_SIZE;
+  CUtensorMap mx, mw;
+  int st = make_map(&mx, x, n_rows, k_dim, G_BM);
+  if (st) return st;
+  st = make_map(&mw, w, epilogue ? 2 * out_features : out_features, k_dim, G_BN);
+  if (st) return st;
+  if (out_dtype == IFB_BF16)
+    return epilogue ? tc_launch<1, bf16>(mx, mw, out, n_rows, out_features, k_dim, err, stream)
+                    : tc_launch<0, bf16>(mx, mw, out, n_rows, out_features, k_dim, err, stream);
+  if (out_dtype == IFB_F32)
+    return epilogue ? tc_launch<1, float>(mx, mw, out, n_rows, out_features, k_dim, err, stream)
+                    : tc_launch<0, float>(mx, mw, out, n_rows, out_features, k_dim, err, stream);
+  return IFB_ERR_DTYPE;
+}

@@ -19,7 +19,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 from ..errors import OutOfPages
-from ..sampling import Sampler
+from ..sampling import Sampler, uniform
 from ..tokenizer import StreamingDetokenizer, Tokenizer, check_stop_strings
 from .loading import EngineOptions, build_runner
 from .request import Request, RequestMetrics, RequestState, SamplingParams
@@ -54,7 +54,7 @@ class Engine:
         self.runner = runner
         self.scheduler = scheduler or Scheduler(runner.cache, runner.max_requests, runner.max_tokens,
                                                 runner.max_model_len, max_prefill_portion)
-        self.sampler = sampler or Sampler(runner.rt.kernels, runner.rt.device)
+        self.sampler = sampler or Sampler(runner.rt.kernels, runner.rt.device)   # for callers that hold logits
         self.tokenizer = tokenizer
         self.eos_token_ids = list(eos_token_ids)
         self._detoks: Dict[str, StreamingDetokenizer] = {}
@@ -136,14 +136,14 @@ class Engine:
             return raw
         entries = [StepEntry(e.request_id, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan.entries]
         try:
-            logits = self.runner.step(entries)
             sampled = [e for e in plan.entries if e.sample]
+            reqs = [self.scheduler.get_request(e.request_id) for e in sampled]
+            temps = [r.sampling_params.effective_temperature for r in reqs]
+            us = [uniform(r.sampling_params.seed, len(r.output_token_ids)) if t > 0.0 else 0.0
+                  for r, t in zip(reqs, temps)]
+            ids = self.runner.step_and_sample(entries, temps, us)
             if sampled:
-                reqs = [self.scheduler.get_request(e.request_id) for e in sampled]
-                toks = self.sampler.sample(
-                    logits, [r.sampling_params.effective_temperature for r in reqs],
-                    [r.sampling_params.seed for r in reqs], [len(r.output_token_ids) for r in reqs])
-                raw.tokens = {e.request_id: int(t) for e, t in zip(sampled, toks)}
+                raw.tokens = {e.request_id: int(t) for e, t in zip(sampled, ids.tolist())}
         except Exception as e:  # a failed step fails its requests, not the engine
             if not isinstance(e, OutOfPages):
                 traceback.print_exc()

@@ -59,6 +59,7 @@ class _Arena:
     def __init__(self, device, max_rows):
         self.device, self.max_rows = device, max_rows
         self._bufs: Dict[tuple, torch.Tensor] = {}
+        self.generation = 0          # bumped whenever a buffer is (re)allocated: captured graphs go stale
 
     def get(self, name, shape, dtype, rows=None):
         cap = max(rows or self.max_rows, shape[0])
@@ -67,6 +68,7 @@ class _Arena:
         if buf is None or buf.shape[0] < cap:
             buf = torch.empty((cap, *shape[1:]), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.generation += 1
         return buf[: shape[0]]
 
 
@@ -122,7 +124,7 @@ class ModelRunner:
         self._pin = dev is not None and torch.device(dev).type == "cuda"
         n, r, g = max_tokens, self.max_requests, len(cache.kv_groups)
         # one staging area: [ids n][pos n][req n][logit_rows n][cu_q r+1][seq r][slot r][first r] + g * [slots n]
-        self._small_len = 4 * n + 4 * r + 1 + g * n
+        self._small_len = 4 * n + 4 * r + 1 + g * n + 2 * r      # the last 2r words: temperatures, uniforms (float32)
         # two host staging sets used in turn: a set is rewritten only after the copy that
         # read it last has finished (its event), so the host may run a step ahead
         self._stage = [
@@ -133,6 +135,12 @@ class ModelRunner:
         self._dev_small = torch.zeros(self._small_len, dtype=torch.int32, device=dev)
         self._dev_tables = torch.full((max(g, 1), r, self.max_pages), RELEASED, dtype=torch.int32, device=dev)
         self.steps_run = 0
+        self.sampled = torch.zeros(max(r, 1), dtype=torch.int32, device=dev)
+        # decode-only steps are replayed from CUDA graphs, one per (batch bucket, context bucket)
+        self.use_graphs = self._pin and bool(getattr(model, "graph_safe", False))
+        self._graphs: Dict[tuple, tuple] = {}
+        self.graph_replays = 0
+        self.launches_per_graph_step = 0
 
     # ------------------------------------------------------------------ the step
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -164,13 +172,7 @@ class ModelRunner:
         if total > self.max_tokens:
             raise BatchError(f"{total} tokens in a step; at most {self.max_tokens}")
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Run one batch.  Returns float32 logits ``[wanted, vocab]`` on the device (None if
-        nothing is wanted).  The returned tensor is a buffer that the next step overwrites.
-
-        Raises :class:`OutOfPages`, with nothing changed, if the pages for the step's tokens
-        cannot all be had."""
-        self.validate(entries)
+    def _reserve(self, entries) -> None:
         cache = self.cache
         done = []
         try:
@@ -181,15 +183,89 @@ class ModelRunner:
             for e in done:
                 cache.release_allocation(e.request_id)
             raise
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns float32 logits ``[wanted, vocab]`` on the device (None if
+        nothing is wanted).  The returned tensor is a buffer that the next step overwrites.
+
+        Raises :class:`OutOfPages`, with nothing changed, if the pages for the step's tokens
+        cannot all be had."""
+        self.validate(entries)
+        self._reserve(entries)
         ctx = self._build_context(entries)
         logits = self.model.forward(ctx)
         for e in entries:
-            cache.commit(e.request_id, len(e.tokens))
+            self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
         return logits
 
+    def step_and_sample(self, entries: Sequence[StepEntry], temperatures: Sequence[float],
+                        uniforms: Sequence[float]) -> Optional[torch.Tensor]:
+        """``step`` followed by the sampling kernel on the wanted rows: returns the int32 token
+        ids on the device (None if nothing is wanted).  ``temperatures`` and ``uniforms`` have
+        one entry per wanted row.  A step in which every request brings one token and wants its
+        logits (plain decoding) is replayed from a CUDA graph."""
+        self.validate(entries)
+        wanted = sum(len(e.want) for e in entries)
+        if len(temperatures) != wanted or len(uniforms) != wanted:
+            raise BatchError("one temperature and one uniform number per wanted row")
+        self._reserve(entries)
+        decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        greedy = all(t == 0.0 for t in temperatures)
+        if self.use_graphs and decode_only:
+            self._graph_step(entries, temperatures, uniforms, greedy)
+        else:
+            ctx = self._build_context(entries, temperatures=temperatures, uniforms=uniforms)
+            self._forward_and_sample(ctx, greedy)
+        for e in entries:
+            self.cache.commit(e.request_id, len(e.tokens))
+        self.steps_run += 1
+        return self.sampled[:wanted] if wanted else None
+
+    def _forward_and_sample(self, ctx, greedy: bool):
+        logits = self.model.forward(ctx)
+        if logits is not None:
+            m = logits.shape[0]
+            if greedy:
+                self.rt.kernels.sample(logits, None, None, self.sampled[:m])
+            else:
+                self.rt.kernels.sample(logits, ctx.temperatures[:m], ctx.uniforms[:m], self.sampled[:m])
+        return logits
+
+    def _graph_step(self, entries, temperatures, uniforms, greedy) -> None:
+        r = len(entries)
+        r_bucket = 1
+        while r_bucket < r:
+            r_bucket *= 2
+        r_bucket = min(r_bucket, self.max_requests)
+        longest = max(self.cache.num_computed(e.request_id) + 1 for e in entries)
+        seq_bucket = 256
+        while seq_bucket < longest:
+            seq_bucket *= 2
+        key = (r_bucket, seq_bucket, greedy)
+        ctx = self._build_context(entries, temperatures=temperatures, uniforms=uniforms, pad_to=r_bucket,
+                                  seq_bucket=seq_bucket)
+        stamp = (self.arena.generation, getattr(self.rt.kernels, "scratch_generation", 0))
+        held = self._graphs.get(key)
+        if held is not None and held[1] == stamp:
+            held[0].replay()
+            self.graph_replays += 1
+            return
+        # first time (or buffers moved since): run once as it is, which also makes every allocation,
+        # then record the same launches for the next time
+        self._forward_and_sample(ctx, greedy)
+        torch.cuda.synchronize()
+        stamp = (self.arena.generation, getattr(self.rt.kernels, "scratch_generation", 0))
+        graph = torch.cuda.CUDAGraph()
+        before = getattr(self.rt.kernels, "launches", 0)
+        with torch.cuda.graph(graph):
+            self._forward_and_sample(ctx, greedy)
+        self.launches_per_graph_step = getattr(self.rt.kernels, "launches", 0) - before
+        # the recording ran nothing; this step's result is the eager run's
+        self._graphs[key] = (graph, stamp)
+
     # ------------------------------------------------------------------ metadata
-    def _build_context(self, entries) -> StepContext:
+    def _build_context(self, entries, temperatures=None, uniforms=None, pad_to=0, seq_bucket=0) -> StepContext:
         cache = self.cache
         n_max, r_max = self.max_tokens, self.max_requests
         turn = self.steps_run % 2
@@ -217,7 +293,13 @@ class ModelRunner:
                 table = cache.block_table(e.request_id, gi)
                 row = host_tables[gi, r]
                 row[: len(table)] = torch.tensor(table, dtype=torch.int32)
-        N, R, M = len(ids), len(entries), len(rows)
+        real_rows = len(rows)
+        for j in range(len(entries), pad_to):      # padding of a graph bucket: tokens that store and see nothing
+            ids.append(0); pos.append(0); req.append(j); rows.append(0)
+            cu.append(cu[-1] + 1); seq.append(0); slots.append(0); first.append(0)
+            for gs in group_slots:
+                gs.append(-1)
+        N, R, M = len(ids), len(cu) - 1, len(rows)
         h = host_small
         o_ids, o_pos, o_req, o_rows = 0, n_max, 2 * n_max, 3 * n_max
         o_cu = 4 * n_max
@@ -236,6 +318,15 @@ class ModelRunner:
         h[o_first:o_first + R] = torch.tensor(first, dtype=torch.int32)
         for gi, gs in enumerate(group_slots):
             h[o_g + gi * n_max: o_g + gi * n_max + N] = torch.tensor(gs, dtype=torch.int32)
+        o_f = o_g + len(group_slots) * n_max
+        if temperatures is not None:
+            hf = h.view(torch.float32)
+            k = len(temperatures)
+            hf[o_f:o_f + r_max] = 0.0
+            hf[o_f + r_max:o_f + 2 * r_max] = 0.0
+            if k:
+                hf[o_f:o_f + k] = torch.tensor(list(map(float, temperatures)), dtype=torch.float32)
+                hf[o_f + r_max:o_f + r_max + k] = torch.tensor(list(map(float, uniforms)), dtype=torch.float32)
         d = self._dev_small
         d.copy_(h, non_blocking=True)
         if cache.kv_groups:
@@ -246,7 +337,10 @@ class ModelRunner:
             self._stage_events[turn] = ev
         ctx = StepContext(self)
         ctx.num_tokens, ctx.num_requests, ctx.num_logit_rows = N, R, M
-        ctx.max_q_len, ctx.max_seq_len = max_q, max(seq)
+        ctx.max_q_len, ctx.max_seq_len = max_q, max(max(seq), seq_bucket)
+        df = d.view(torch.float32)
+        ctx.temperatures, ctx.uniforms = df[o_f:o_f + r_max], df[o_f + r_max:o_f + 2 * r_max]
+        ctx.num_real_logit_rows = real_rows
         ctx.token_ids, ctx.positions = d[o_ids:o_ids + N], d[o_pos:o_pos + N]
         ctx.req_index, ctx.logit_rows = d[o_req:o_req + N], d[o_rows:o_rows + M]
         ctx.cu_q, ctx.seq_lens = d[o_cu:o_cu + R + 1], d[o_seq:o_seq + R]

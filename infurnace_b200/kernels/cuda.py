@@ -58,6 +58,7 @@ class CudaKernels:
             raise KernelError("no CUDA device is available; this engine has no CPU path")
         self._progress = progress
         self.launches = 0          # kernels launched through this object
+        self.scratch_generation = 0  # bumped when a scratch buffer moves: captured graphs go stale
         self.core = load_library("core", progress=progress)
         c = self.core
         c.ifb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
@@ -157,8 +158,10 @@ class CudaKernels:
             self.core.ifb_linear_skinny_scratch(n, o, epi, splits, ctypes.byref(nf), ctypes.byref(nc))
             if self._lin_partials is None or self._lin_partials.numel() < nf.value:
                 self._lin_partials = torch.empty(max(nf.value, 1 << 20), dtype=torch.float32, device="cuda")
+                self.scratch_generation += 1
             if self._lin_counters is None or self._lin_counters.numel() < nc.value:
                 self._lin_counters = torch.zeros(max(nc.value, 1 << 14), dtype=torch.int32, device="cuda")
+                self.scratch_generation += 1
             partials, counters = self._lin_partials, self._lin_counters
         self.launches += 1
         _check(self.core.ifb_linear_skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), _ptr(partials),
@@ -235,15 +238,17 @@ class CudaKernels:
         return lib
 
     def attention_splits(self, num_requests, num_kv_heads, max_seq_len, window=0):
-        """How many CTAs share one (request, key/value head) of the small-q kernel: enough to
-        give every SM two CTAs, and no fewer than 256 keys per split."""
+        """How many CTAs share one (request, key/value head) of the small-q kernel: as many as
+        keep the whole grid resident at once (two CTAs fit on an SM), so that no second wave
+        runs, and no fewer than 256 keys per split."""
         reach = min(max_seq_len, window + 16) if window else max_seq_len
-        want = -(-2 * self.sm_count // max(1, num_requests * num_kv_heads))
-        return max(1, min(want, -(-reach // 256), 32))
+        fit = (2 * self.sm_count) // max(1, num_requests * num_kv_heads)
+        return max(1, min(fit, -(-reach // 256), 32))
 
     def attention_scratch(self, floats):
         if self._attn_scratch is None or self._attn_scratch.numel() < floats:
             self._attn_scratch = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device="cuda")
+            self.scratch_generation += 1
         return self._attn_scratch
 
     def _paged_attention_mma(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out,

@@ -18,6 +18,8 @@ class PagedAttention:
     cutting the work: the query at position p sees the keys at positions <= p
     (model.py:117-132 has three cases for the same rule)."""
 
+    graph_safe = True     # launches depend on the step's sizes only, never on values read on the host
+
     def __init__(self, spec: AttentionSpec, weights, runtime):
         self.spec = spec
         self.rt = runtime

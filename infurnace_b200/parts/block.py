@@ -19,6 +19,10 @@ class PreNormBlock:
         self.ffn_norm = build_part(spec.ffn_norm, weights, runtime)
         self.ffn = build_part(spec.ffn, weights, runtime)
 
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn))
+
     def forward(self, x, pending, ctx, call):
         h = ctx.buffer("h", x.shape, self.rt.act_dtype)
         self.mixer_norm.forward(x, h, delta=pending)

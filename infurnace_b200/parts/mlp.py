@@ -13,6 +13,8 @@ class GatedMLP:
     gate and up run as one product against their row-wise concatenation (exact), with the
     activation and the product of the two halves in that kernel's epilogue."""
 
+    graph_safe = True     # launches depend on the step's sizes only, never on values read on the host
+
     def __init__(self, spec: GatedMLPSpec, weights, runtime):
         if spec.activation != "silu":
             raise ModelConfigError(f"activation {spec.activation!r}: only 'silu' has a kernel")

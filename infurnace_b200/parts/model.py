@@ -53,6 +53,12 @@ class DecoderModel:
         self.final_norm = build_part(plan.final_norm, weights, runtime)
         self.lm_head = build_part(plan.lm_head, weights, runtime)
 
+    @property
+    def graph_safe(self) -> bool:
+        """True when every layer's launches depend only on the sizes of a step, so that a
+        decode step may be recorded once and replayed (a part says so with ``graph_safe``)."""
+        return all(getattr(layer, "graph_safe", False) for layer in self.layers)
+
     def forward(self, ctx):
         n = ctx.num_tokens
         x = ctx.buffer("x", (n, self.plan.hidden_size), torch.float32)

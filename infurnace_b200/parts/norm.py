@@ -11,6 +11,8 @@ class RMSNorm:
     without ``rows`` the sum is written back to x, which is the reference's ``x = x + ...``
     (model.py:143,148) done in the same pass."""
 
+    graph_safe = True     # launches depend on the step's sizes only, never on values read on the host
+
     def __init__(self, spec: RMSNormSpec, weights, runtime):
         self.spec = spec
         self.weight = weights[spec.weight]

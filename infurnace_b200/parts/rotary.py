@@ -14,6 +14,8 @@ class Rotary:
     inside the attention part's fused kernel, which takes the frequencies, the rotated
     width and the pairing as arguments (model.py:24-27 is the half-split pairing)."""
 
+    graph_safe = True     # launches depend on the step's sizes only, never on values read on the host
+
     def __init__(self, spec: RotarySpec, weights, runtime):
         if spec.rotary_dim % 2 or not 0 < spec.rotary_dim <= spec.head_dim:
             raise ModelConfigError(f"rotary_dim {spec.rotary_dim} must be even and at most head_dim {spec.head_dim}")

@@ -98,14 +98,15 @@ def test_out_of_pages_fails_the_lone_request_and_frees_everything(models):
 def test_a_failing_step_fails_its_requests_and_the_engine_goes_on(models, monkeypatch, capsys):
     eng = engine(models["A"], "A")
     eng.add_request(Request("a", [1, 2, 3], SamplingParams(max_tokens=4)))
-    real = eng.runner.step
-    monkeypatch.setattr(eng.runner, "step", lambda entries: (_ for _ in ()).throw(RuntimeError("device fell over")))
+    real = eng.runner.step_and_sample
+    monkeypatch.setattr(eng.runner, "step_and_sample",
+                        lambda *a: (_ for _ in ()).throw(RuntimeError("device fell over")))
     res = eng.step()
     assert res.failed_requests == ("a",)
     a = eng.scheduler.get_request("a")
     assert a.state is RequestState.FAILED and "device fell over" in a.error
     assert eng.runner.cache.free_pages() == [40] and eng.is_done()
-    monkeypatch.setattr(eng.runner, "step", real)
+    monkeypatch.setattr(eng.runner, "step_and_sample", real)
     assert len(eng.generate([[4, 5, 6]], SamplingParams(max_tokens=3))[0]) == 3
 
 

@@ -1,0 +1,127 @@
+"""Generation through the entry points on the GPU: greedy and temperature sampling against the
+plain implementation, decode steps replayed from CUDA graphs, preemption, and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen3 as P
+import tiny
+from infurnace_b200.engine import Engine, EngineOptions, Request, RequestState, SamplingParams, generate
+from infurnace_b200.sampling import uniform
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = str(tmp_path_factory.mktemp("models"))
+    return {n: tiny.make_model_dir(n, root) for n in tiny.TINY}
+
+
+def engine(model_dir, name, dtype, **kw):
+    opts = dict(dtype=dtype, page_size=tiny.TINY[name]["page_size"], num_pages=64, max_num_seqs=4,
+                max_num_batched_tokens=64)
+    opts.update(kw)
+    return Engine.from_model_dir(model_dir, EngineOptions(**opts))
+
+
+def near_top(cfg, w, prompt, tokens, margin):
+    """Every generated token is, given its own prefix, within ``margin`` of the plain top logit."""
+    seq = list(prompt)
+    for t in tokens:
+        logits = P.forward(cfg, w, seq)[-1]
+        assert float(logits.max() - logits[t]) <= margin, (len(seq), t, int(logits.argmax()))
+        seq.append(t)
+
+
+@pytest.mark.parametrize("name", list(tiny.TINY))
+def test_greedy_float32_equals_the_plain_implementation(models, name):
+    cfg, w = P.read_model(models[name])
+    eng = engine(models[name], name, "float32")
+    prompts = [tiny.random_tokens(cfg["vocab_size"], n, 50 + n) for n in (1, 7, 33)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=16))
+    for p, o in zip(prompts, outs):
+        want = P.greedy(cfg, w, p, 16)
+        if o != want:
+            near_top(cfg, w, p, o, 1e-5)       # only an exact tie in float32 may part them
+    assert eng.runner.graph_replays > 0          # decode steps came from graphs
+    eng.runner.cache.check()
+
+
+@pytest.mark.parametrize("name", list(tiny.TINY))
+def test_greedy_bfloat16_stays_at_the_top(models, name):
+    cfg, w = P.read_model(models[name])
+    eng = engine(models[name], name, "bfloat16")
+    prompts = [tiny.random_tokens(cfg["vocab_size"], n, 60 + n) for n in (1, 7, 33, 100)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=16))
+    for p, o in zip(prompts, outs):
+        assert len(o) == 16
+        near_top(cfg, w, p, o, 0.05)
+    assert eng.runner.graph_replays > 0
+
+
+def test_graph_replay_equals_eager_steps(models):
+    a = engine(models["B"], "B", "bfloat16")
+    b = engine(models["B"], "B", "bfloat16")
+    b.runner.use_graphs = False
+    prompts = [tiny.random_tokens(320, n, 70 + n) for n in (5, 19, 64)]
+    sp = SamplingParams(max_tokens=40, temperature=0.7, seed=3)
+    assert a.generate(prompts, sp) == b.generate(prompts, sp)
+    assert a.runner.graph_replays > 0 and b.runner.graph_replays == 0
+
+
+def test_temperature_sampling_follows_the_requests_own_numbers(models):
+    cfg, w = P.read_model(models["B"])
+    prompts = [tiny.random_tokens(320, n, 20 + n) for n in (5, 19, 64, 100)]
+    sps = [SamplingParams(max_tokens=12, temperature=0.8, seed=100 + i) for i in range(4)]
+    eng = engine(models["B"], "B", "float32", max_num_batched_tokens=16)      # portions of 16 beside decode tokens
+    together = eng.generate(prompts, sps)
+    alone = [engine(models["B"], "B", "float32", max_num_batched_tokens=256).generate([p], sp)[0]
+             for p, sp in zip(prompts, sps)]
+    assert together == alone
+    for p, sp, out in zip(prompts, sps, together):
+        seq = list(p)
+        for k, t in enumerate(out):
+            probs = P.temperature_probs(P.forward(cfg, w, seq)[-1], 0.8).double().cumsum(0)
+            u = uniform(sp.seed, k)
+            want = int(torch.searchsorted(probs, torch.tensor(u, dtype=torch.float64), right=True))
+            if t != want:     # u may sit on a boundary of the running sum
+                assert abs(t - want) == 1 and min(abs(float(probs[t]) - u), abs(float(probs[want]) - u)) < 1e-4
+            seq.append(t)
+
+
+def test_preemption_round_trip_on_the_gpu(models):
+    cfg, w = P.read_model(models["A"])
+    prompts = [tiny.random_tokens(256, n, 30 + n) for n in (30, 28, 25)]
+    small = engine(models["A"], "A", "float32", num_pages=6)
+    outs = small.generate(prompts, SamplingParams(max_tokens=30))
+    assert small.scheduler.num_preemptions > 0
+    roomy = engine(models["A"], "A", "float32").generate(prompts, SamplingParams(max_tokens=30))
+    assert outs == roomy
+    small.runner.cache.check()
+    assert small.runner.cache.free_pages() == [6]
+
+
+def test_tool_style_entry_point_and_command_line(models, tmp_path):
+    eng = engine(models["A"], "A", "bfloat16")
+    toks, timings = generate(eng, [5, 6, 7], 4)
+    assert len(toks) == 7 and timings["prefill_ms"] > 0 and len(timings["decode_times_ms"]) == 3
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bin", "infurnace-b200"), "--model", models["A"],
+                          "--prompt-ids", "5,6,7", "--max-tokens", "4", "--json", "--page-size", "16",
+                          "--max-context", "64"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    report = json.loads(out.stdout)
+    assert report["prompt"] == [5, 6, 7] and report["generated_token_ids"] == toks[3:]
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(tiny.TINY["B"]["config"]))
+    out = subprocess.run([sys.executable, "-m", "infurnace_b200", "--random-weights", "3", "--config", str(cfg_path),
+                          "--prompt", "hello", "--char-tokenizer", "--max-tokens", "5", "--page-size", "8",
+                          "--max-context", "64", "--temperature", "0.9", "--seed", "4"],
+                         capture_output=True, text=True, timeout=300, cwd=root)
+    assert out.returncode == 0, out.stderr
+    assert len(out.stdout.rstrip("\n")) == 5
