@@ -144,6 +144,9 @@ class Engine:
             ids = self.runner.step_and_sample(entries, temps, us)
             if sampled:
                 raw.tokens = {e.request_id: int(t) for e, t in zip(sampled, ids.tolist())}
+            check = getattr(self.runner.rt.kernels, "check_device_errors", None)
+            if check is not None:
+                check()
         except Exception as e:  # a failed step fails its requests, not the engine
             if not isinstance(e, OutOfPages):
                 traceback.print_exc()

@@ -30,6 +30,7 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"
 # library name -> (sources, extra flags)
 LIBRARIES: Dict[str, tuple] = {
     "core": (["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "linear_skinny.cu"], []),
+    "linear_tcgen05": (["linear_tcgen05.cu"], []),
     # compiled once per head size: defines={"HEAD_DIM": d}
     "attention_mma": (["attention_mma.cu"], []),
 }
@@ -147,6 +148,6 @@ def load_library(name: str, defines: Optional[Dict[str, object]] = None, progres
 def build_all(progress=None) -> List[str]:
     """Compile every library (used by the build check; needs no GPU)."""
     from concurrent.futures import ThreadPoolExecutor
-    jobs = [("core", None)] + DEFAULT_VARIANTS
+    jobs = [("core", None), ("linear_tcgen05", None)] + DEFAULT_VARIANTS
     with ThreadPoolExecutor(max_workers=4) as pool:
         return list(pool.map(lambda j: compile_library(j[0], j[1], progress), jobs))

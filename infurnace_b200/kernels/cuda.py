@@ -77,6 +77,10 @@ class CudaKernels:
         self._lin_partials = None
         self._lin_counters = None
         self.skinny_max_rows = 4096    # above this the plain kernel runs (until a large-tile kernel takes over)
+        self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
+        self._tc_err = None            # device int: non-zero after a bounded wait in a tcgen05 kernel gave up
+        self._tc_used = False
+        self.tc_min_rows = 65
         self._attn_mma = {}        # head size -> library
         self._attn_scratch = None
         self.sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
@@ -135,12 +139,35 @@ class CudaKernels:
         epi = {"none": 0, "silu_gate": 1}[epilogue]
         if w.shape[1] != k or out.shape[0] != n or w.shape[0] != (2 * o if epi else o):
             raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not match")
-        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 and n <= self.skinny_max_rows \
+        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 \
                 and out.dtype in (torch.bfloat16, torch.float32):
+            if n >= self.tc_min_rows:
+                return self._linear_tcgen05(x, w, out, n, o, k, epi)
             return self._linear_skinny(x, w, out, n, o, k, epi)
         self.launches += 1
         _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
                                          n, o, k, epi, self._stream()), "linear")
+
+    def _linear_tcgen05(self, x, w, out, n, o, k, epi):
+        if self._tc is None:
+            self._tc = load_library("linear_tcgen05", progress=self._progress)
+            self._tc.ifb_linear_tcgen05.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                    c_void_p, c_void_p]
+            self._tc_err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.launches += 1
+        self._tc_used = True
+        _check(self._tc.ifb_linear_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), n, o, k, epi,
+                                           self._tc_err.data_ptr(), self._stream()), "linear")
+
+    def check_device_errors(self):
+        """Raise if a kernel recorded that one of its bounded waits gave up (synchronises)."""
+        if self._tc_used:
+            self._tc_used = False
+            code = int(self._tc_err.item())
+            if code:
+                self._tc_err.zero_()
+                raise KernelError(f"a tcgen05 product gave up waiting on a barrier (code {code}: 1 producer, 2 issuer, "
+                                  "3 epilogue); its output is not valid")
 
     def linear_splits(self, n, o, k):
         """CTAs that share the k range of one 64-feature tile: enough to cover the SMs twice, and
