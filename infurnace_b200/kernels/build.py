@@ -79,10 +79,23 @@ def build_dir() -> str:
         return _build_dir
 
 
+def _closure(sources: Sequence[str]) -> List[str]:
+    """The sources and every file of csrc that they include with quotes, directly or not."""
+    import re
+    seen, todo = [], list(sources)
+    while todo:
+        name = todo.pop(0)
+        if name in seen or not os.path.exists(os.path.join(CSRC, name)):
+            continue
+        seen.append(name)
+        with open(os.path.join(CSRC, name), "r", encoding="utf-8") as f:
+            todo.extend(re.findall(r'^\s*#\s*include\s*"([^"]+)"', f.read(), flags=re.M))
+    return seen
+
+
 def _hash(sources: Sequence[str], flags: Sequence[str]) -> str:
     h = hashlib.sha256()
-    headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
-    for name in list(sources) + headers:
+    for name in _closure(sources):
         with open(os.path.join(CSRC, name), "rb") as f:
             h.update(name.encode() + b"\0" + f.read())
     h.update(" ".join(list(ARCH_FLAGS) + list(BASE_FLAGS) + list(flags)).encode())
