@@ -31,6 +31,8 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"
 LIBRARIES: Dict[str, tuple] = {
     "core": (["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "linear_skinny.cu"], []),
     "linear_tcgen05": (["linear_tcgen05.cu"], []),
+    # the few-rows product with its scratch inside the library, for callers that must not allocate
+    "linear_skinny_static": (["linear_skinny_static.cu"], []),
     # compiled once per head size: defines={"HEAD_DIM": d}
     "attention_mma": (["attention_mma.cu"], []),
 }
@@ -161,6 +163,6 @@ def load_library(name: str, defines: Optional[Dict[str, object]] = None, progres
 def build_all(progress=None) -> List[str]:
     """Compile every library (used by the build check; needs no GPU)."""
     from concurrent.futures import ThreadPoolExecutor
-    jobs = [("core", None), ("linear_tcgen05", None)] + DEFAULT_VARIANTS
+    jobs = [("core", None), ("linear_tcgen05", None), ("linear_skinny_static", None)] + DEFAULT_VARIANTS
     with ThreadPoolExecutor(max_workers=4) as pool:
         return list(pool.map(lambda j: compile_library(j[0], j[1], progress), jobs))
