@@ -196,6 +196,8 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][DP]
   bf16* KV = Qs + 16 * DP;                                   // SQ_STAGES x (K [BN][DP], V [BN][DP])
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = nq / nkv;
@@ -308,6 +310,8 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   const int* __restrict__ cu_q, bf16* __restrict__ out, int n_tokens, int n_req, int nq,
                                   int nkv, int num_splits) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= n_tokens * nq) return;
   const int tok = warp / nq;
@@ -340,6 +344,8 @@ attn_tile_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __res
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [64][DP]
   bf16* KV = Qs + 64 * DP;
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   const int kvh = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = nq / nkv;
@@ -455,26 +461,23 @@ IFB_EXPORT int ifb_attention_mma(const void* qkv, int row_stride, const void* pa
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_tokens * nq * num_splits * D : nullptr;
     dim3 grid(num_splits, nkv, n_req);
-    attn_small_q_kernel<<<grid, THREADS, small_q_smem(), stream>>>(
-        (const bf16*)qkv, row_stride, (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, part_o,
-        part_ml, nq, nkv, page_size, scale_log2, window, num_splits);
-    int st = ifb_launch_status();
+    int st = ifb_launch(attn_small_q_kernel, grid, dim3(THREADS), small_q_smem(), stream, (const bf16*)qkv, row_stride,
+                        (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, part_o, part_ml, nq, nkv,
+                        page_size, scale_log2, window, num_splits);
     if (st) return st;
     if (num_splits > 1) {
       const long long warps = (long long)n_tokens * nq;
-      attn_merge_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(part_o, part_ml, cu_q, (bf16*)out, n_tokens,
-                                                                        n_req, nq, nkv, num_splits);
-      st = ifb_launch_status();
+      st = ifb_launch(attn_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
+                      (const float*)part_ml, cu_q, (bf16*)out, n_tokens, n_req, nq, nkv, num_splits);
       if (st) return st;
     }
   }
   if (run_tiles) {
     const int tpc = 4 * (16 / G);
     dim3 grid((max_q_len + tpc - 1) / tpc, nkv, n_req);
-    attn_tile_kernel<<<grid, THREADS, tile_smem(), stream>>>((const bf16*)qkv, row_stride, (const bf16*)pages,
-                                                            block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, nq, nkv,
-                                                            page_size, scale_log2, window);
-    return ifb_launch_status();
+    return ifb_launch(attn_tile_kernel, grid, dim3(THREADS), tile_smem(), stream, (const bf16*)qkv, row_stride,
+                      (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, nq, nkv, page_size,
+                      scale_log2, window);
   }
   return IFB_OK;
 }

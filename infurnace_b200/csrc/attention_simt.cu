@@ -18,6 +18,8 @@ paged_attention_simt_kernel(const T* __restrict__ qkv, int row_stride, const T* 
                             const int* __restrict__ seq_lens, T* __restrict__ out, int n_tokens, int n_req, int nq,
                             int nkv, int d, int page_size, float scale, int window) {
   extern __shared__ float sm[];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * warps + warp;
   if (item >= (long long)n_tokens * nq) return;
@@ -93,14 +95,12 @@ IFB_EXPORT int ifb_paged_attention_simt(const void* qkv, int dtype, int row_stri
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
   if (dtype == IFB_F32)
-    paged_attention_simt_kernel<float><<<blocks, warps * 32, smem, stream>>>(
-        (const float*)qkv, row_stride, (const float*)pages, block_tables, bt_stride, cu_q, seq_lens, (float*)out,
-        n_tokens, n_req, nq, nkv, d, page_size, scale, window);
-  else if (dtype == IFB_BF16)
-    paged_attention_simt_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
-        (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)pages, block_tables, bt_stride, cu_q, seq_lens,
-        (__nv_bfloat16*)out, n_tokens, n_req, nq, nkv, d, page_size, scale, window);
-  else
-    return IFB_ERR_DTYPE;
-  return ifb_launch_status();
+    return ifb_launch(paged_attention_simt_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream, (const float*)qkv,
+                      row_stride, (const float*)pages, block_tables, bt_stride, cu_q, seq_lens, (float*)out, n_tokens, n_req,
+                      nq, nkv, d, page_size, scale, window);
+  if (dtype == IFB_BF16)
+    return ifb_launch(paged_attention_simt_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream,
+                      (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)pages, block_tables, bt_stride, cu_q,
+                      seq_lens, (__nv_bfloat16*)out, n_tokens, n_req, nq, nkv, d, page_size, scale, window);
+  return IFB_ERR_DTYPE;
 }

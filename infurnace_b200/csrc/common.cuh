@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define IFB_F32 0
 #define IFB_BF16 1
@@ -20,6 +21,43 @@
 static inline int ifb_launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? IFB_OK : -(int)e;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of these libraries is launched so that it may be
+// scheduled while the kernel before it in the stream is still finishing: launch latency and the
+// kernel's own set-up then overlap the predecessor's tail.  The price is a rule that every kernel
+// keeps: nothing that a predecessor may have written is read, and nothing at all is written, before
+// ifb_pdl_wait(), which returns once every kernel before this one has completed and its writes
+// are visible.  What may come before the wait is work on constants (weights), such as asking the
+// L2 cache to fetch them.  ifb_pdl_trigger() lets the next kernel in the stream start being
+// scheduled; it is called right after the wait, so that one kernel, not the rest of the graph, runs
+// ahead and sits on the SMs.  IFB_PDL=0 in the environment turns the launch attribute off.
+__device__ __forceinline__ void ifb_pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void ifb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void ifb_prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p)); }
+
+static inline bool ifb_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("IFB_PDL"); on = (e && e[0] == '0') ? 0 : 1; }
+  return on != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int ifb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ifb_pdl_enabled() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+  if (e != cudaSuccess) { cudaGetLastError(); return -(int)e; }
+  return IFB_OK;
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);

@@ -9,6 +9,8 @@
 // ------------------------------------------------------------------------------------------
 __global__ void embed_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ ids,
                              float* __restrict__ out, int hidden) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   const int n = blockIdx.x;
   const size_t row = (size_t)ids[n] * hidden;
   for (int h = threadIdx.x; h < hidden; h += blockDim.x)
@@ -19,8 +21,7 @@ IFB_EXPORT int ifb_embed(const void* table, int table_dtype, const int* ids, flo
                          cudaStream_t stream) {
   if (n <= 0) return IFB_OK;
   if (table_dtype != IFB_F32 && table_dtype != IFB_BF16) return IFB_ERR_DTYPE;
-  embed_kernel<<<n, 256, 0, stream>>>(table, table_dtype, ids, out, hidden);
-  return ifb_launch_status();
+  return ifb_launch(embed_kernel, dim3(n), dim3(256), 0, stream, table, table_dtype, ids, out, hidden);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -33,6 +34,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                                void* __restrict__ out, int out_dtype, const int* __restrict__ rows, int hidden) {
   extern __shared__ float vbuf[];
   __shared__ float scratch[33];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   const int orow = blockIdx.x;
   const int row = rows ? rows[orow] : orow;
   float* xr = x + (size_t)row * hidden;
@@ -64,9 +67,8 @@ IFB_EXPORT int ifb_rmsnorm(float* x, const float* delta, int num_splits, long lo
     configured = smem;
   }
   const int threads = hidden >= 2048 ? 512 : 256;
-  rmsnorm_kernel<<<num_out_rows, threads, smem, stream>>>(x, delta, delta ? num_splits : 0, (size_t)split_stride, w,
-                                                          w_dtype, eps, out, out_dtype, rows, hidden);
-  return ifb_launch_status();
+  return ifb_launch(rmsnorm_kernel, dim3(num_out_rows), dim3(threads), smem, stream, x, delta, delta ? num_splits : 0,
+                    (size_t)split_stride, w, w_dtype, eps, out, out_dtype, rows, hidden);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -83,6 +85,8 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int n_tokens, int
                                           int interleaved, const int* __restrict__ positions,
                                           const int* __restrict__ slots, T* __restrict__ pages, int page_size) {
   extern __shared__ float sm[];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
   const long long item = (long long)blockIdx.x * warps + warp;
@@ -150,16 +154,14 @@ IFB_EXPORT int ifb_qk_norm_rope_store(void* qkv, int dtype, int n_tokens, int nq
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
   if (dtype == IFB_F32)
-    qk_norm_rope_store_kernel<float><<<blocks, warps * 32, smem, stream>>>(
-        (float*)qkv, n_tokens, nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rotary_dim, interleaved, positions, slots,
-        (float*)pages, page_size);
-  else if (dtype == IFB_BF16)
-    qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
-        (__nv_bfloat16*)qkv, n_tokens, nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rotary_dim, interleaved, positions,
-        slots, (__nv_bfloat16*)pages, page_size);
-  else
-    return IFB_ERR_DTYPE;
-  return ifb_launch_status();
+    return ifb_launch(qk_norm_rope_store_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream, (float*)qkv, n_tokens,
+                      nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rotary_dim, interleaved, positions, slots, (float*)pages,
+                      page_size);
+  if (dtype == IFB_BF16)
+    return ifb_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream,
+                      (__nv_bfloat16*)qkv, n_tokens, nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rotary_dim, interleaved,
+                      positions, slots, (__nv_bfloat16*)pages, page_size);
+  return IFB_ERR_DTYPE;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -175,14 +177,17 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, const
   __shared__ int best_idx[32];
   __shared__ float best_val[32];
   __shared__ int chosen;
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   const int row = blockIdx.x, tid = threadIdx.x, nthreads = blockDim.x;
   const float* l = logits + (size_t)row * vocab;
   const float temp = temperature ? temperature[row] : 0.f;
   const int chunk = (vocab + nthreads - 1) / nthreads;
   const int begin = min(vocab, tid * chunk), end = min(vocab, begin + chunk);
-  // the largest value and its lowest index
+  // the largest value and its lowest index; the row is walked with consecutive threads on consecutive
+  // elements (any partition gives the same answer, since ties go to the lower index)
   float bv = -INFINITY; int bi = 0x7fffffff;
-  for (int i = begin; i < end; ++i) { float v = l[i]; if (v > bv) { bv = v; bi = i; } }
+  for (int i = tid; i < vocab; i += nthreads) { const float v = l[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
   for (int o = 16; o > 0; o >>= 1) {
     float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
     if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
@@ -231,6 +236,5 @@ IFB_EXPORT int ifb_sample(const float* logits, int rows, int vocab, const float*
                           int* out, cudaStream_t stream) {
   if (rows <= 0) return IFB_OK;
   if (vocab < 1) return IFB_ERR_SIZE;
-  sample_kernel<<<rows, 1024, 0, stream>>>(logits, vocab, temperature, uniform, out);
-  return ifb_launch_status();
+  return ifb_launch(sample_kernel, dim3(rows), dim3(1024), 0, stream, logits, vocab, temperature, uniform, out);
 }

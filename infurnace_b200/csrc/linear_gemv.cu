@@ -1,0 +1,173 @@
+// Matrix product for few rows (decoded tokens): out[n, o] = sum_k x[n, k] w[o, k], bfloat16 operands,
+// float32 accumulation on tensor cores (mma.sync m16n8k16 with the weight rows on the M side).
+//
+// A decode step runs a few hundred of these, each over a few megabytes of weights, so what counts is
+// the length of the chain of dependent memory round trips inside one launch, not only the bytes.
+// Hence: a CTA owns 16 output features over the whole k range; its warps split k among themselves and
+// add their partial tiles through shared memory (no partials in global memory, no second pass); weight
+// and activation fragments are loaded straight from global memory into registers, all at once; and the
+// first weight fragments are requested before the kernel waits for its predecessor in the stream,
+// since weights do not depend on it.
+//
+// k is walked in a permuted order inside each MMA: a thread's 16-byte load brings 8 consecutive k of a
+// weight row, which feed two MMAs; the activation fragment is read at the same 8 positions.
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+constexpr int GV_ROWS = 16;
+
+__device__ __forceinline__ uint4 gv_ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void gv_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// NB: blocks of 8 tokens per CTA.  EPI 0: out = y.  EPI 1: w holds gate rows [0, O) and up rows [O, 2O);
+// out = silu(gate) * up.  WARPS: warps of a CTA (they split k).
+template <int NB, int EPI, int WARPS, typename TO>
+__global__ void __launch_bounds__(WARPS * 32)
+linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* __restrict__ out, int n_rows, int o_out,
+                   int k_dim) {
+  extern __shared__ float gv_red[];                 // [WARPS][NE][NB*8][GV_ROWS]
+  constexpr int NE = EPI ? 2 : 1;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane & 3, rr = lane >> 2;
+  const int o0 = blockIdx.x * GV_ROWS, n0 = blockIdx.y * (NB * 8);
+  const int kw = ((k_dim + WARPS - 1) / WARPS + 127) / 128 * 128;      // k per warp, whole 128-wide steps
+  const int kbeg = warp * kw, kend = min(k_dim, kbeg + kw);
+  const bf16* wrow[NE][2];
+#pragma unroll
+  for (int e = 0; e < NE; ++e) {
+    wrow[e][0] = w + (size_t)(e * o_out + min(o0 + rr, o_out - 1)) * k_dim;
+    wrow[e][1] = w + (size_t)(e * o_out + min(o0 + rr + 8, o_out - 1)) * k_dim;
+  }
+  const bf16* xrow[NB];
+  bool xok[NB];
+#pragma unroll
+  for (int j = 0; j < NB; ++j) {
+    const int n = n0 + j * 8 + rr;
+    xok[j] = n < n_rows;
+    xrow[j] = x + (size_t)min(n, n_rows - 1) * k_dim;
+  }
+  float acc[NE][NB][4];
+#pragma unroll
+  for (int e = 0; e < NE; ++e)
+#pragma unroll
+    for (int j = 0; j < NB; ++j) acc[e][j][0] = acc[e][j][1] = acc[e][j][2] = acc[e][j][3] = 0.f;
+
+  bool waited = false;
+  for (int k0 = kbeg; k0 < kend || !waited; k0 += 128) {
+    uint4 wa[NE][4], wb[NE][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int k = k0 + c * 32 + q * 8;
+      const bool in = k < kend;
+#pragma unroll
+      for (int e = 0; e < NE; ++e) {
+        wa[e][c] = in ? gv_ld_stream16(wrow[e][0] + k) : make_uint4(0, 0, 0, 0);
+        wb[e][c] = in ? gv_ld_stream16(wrow[e][1] + k) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    if (!waited) {           // the weights are on their way; now wait for whoever writes x
+      ifb_pdl_wait();
+      ifb_pdl_trigger();
+      waited = true;
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int k = k0 + c * 32 + q * 8;
+      if (k0 + c * 32 >= kend) break;
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        uint4 xv = make_uint4(0, 0, 0, 0);
+        if (xok[j] && k < kend) xv = *reinterpret_cast<const uint4*>(xrow[j] + k);
+#pragma unroll
+        for (int e = 0; e < NE; ++e) {
+          gv_mma(acc[e][j], wa[e][c].x, wb[e][c].x, wa[e][c].y, wb[e][c].y, xv.x, xv.y);
+          gv_mma(acc[e][j], wa[e][c].z, wb[e][c].z, wa[e][c].w, wb[e][c].w, xv.z, xv.w);
+        }
+      }
+    }
+  }
+  // acc[e][j]: c0,c1 -> (feature rr, tokens j*8 + 2q, +1); c2,c3 -> feature rr + 8
+  float* mine = gv_red + (size_t)warp * NE * NB * 8 * GV_ROWS;
+#pragma unroll
+  for (int e = 0; e < NE; ++e)
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int m = rr + (i >> 1) * 8, n = j * 8 + 2 * q + (i & 1);
+        mine[((size_t)e * NB * 8 + n) * GV_ROWS + m] = acc[e][j][i];
+      }
+  __syncthreads();
+  for (int idx = tid; idx < NB * 8 * GV_ROWS; idx += WARPS * 32) {
+    const int n = idx / GV_ROWS, m = idx % GV_ROWS;
+    const int o = o0 + m, tok = n0 + n;
+    if (o >= o_out || tok >= n_rows) continue;
+    float y[NE];
+#pragma unroll
+    for (int e = 0; e < NE; ++e) {
+      float s = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < WARPS; ++wv) s += gv_red[(((size_t)wv * NE + e) * NB * 8 + n) * GV_ROWS + m];
+      y[e] = s;
+    }
+    float r = y[0];
+    if (EPI) r = r / (1.f + expf(-r)) * y[NE - 1];
+    out[(size_t)tok * o_out + o] = from_f32<TO>(r);
+  }
+}
+
+template <int NB, int EPI, int WARPS, typename TO>
+static int gv_launch(const void* x, const void* w, void* out, int n, int o, int k, cudaStream_t s) {
+  const size_t smem = (size_t)WARPS * (EPI ? 2 : 1) * NB * 8 * GV_ROWS * sizeof(float);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(linear_gemv_kernel<NB, EPI, WARPS, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return -(int)e;
+    configured = true;
+  }
+  dim3 grid((o + GV_ROWS - 1) / GV_ROWS, (n + NB * 8 - 1) / (NB * 8));
+  return ifb_launch(linear_gemv_kernel<NB, EPI, WARPS, TO>, grid, dim3(WARPS * 32), smem, s, (const bf16*)x, (const bf16*)w,
+                    (TO*)out, n, o, k);
+}
+
+template <int EPI, int WARPS, typename TO>
+static int gv_by_n(int nb, const void* x, const void* w, void* out, int n, int o, int k, cudaStream_t s) {
+  switch (nb) {
+    case 1: return gv_launch<1, EPI, WARPS, TO>(x, w, out, n, o, k, s);
+    case 2: return gv_launch<2, EPI, WARPS, TO>(x, w, out, n, o, k, s);
+    case 4: return gv_launch<4, EPI, WARPS, TO>(x, w, out, n, o, k, s);
+    default: return gv_launch<8, EPI, WARPS, TO>(x, w, out, n, o, k, s);
+  }
+}
+
+template <int EPI, typename TO>
+static int gv_by_k(int nb, const void* x, const void* w, void* out, int n, int o, int k, cudaStream_t s) {
+  // 128 of k per warp and step: 8 warps cover k up to 1024 in one step, 16 warps up to 2048
+  return k > 1024 ? gv_by_n<EPI, 16, TO>(nb, x, w, out, n, o, k, s) : gv_by_n<EPI, 8, TO>(nb, x, w, out, n, o, k, s);
+}
+
+// x [n_rows, k] and w [out_features (x2 for the silu_gate epilogue), k] bfloat16, 16-byte aligned, k a multiple of 8;
+// out bfloat16 or float32.  Needs no scratch memory.
+IFB_EXPORT int ifb_linear_gemv(const void* x, const void* w, void* out, int out_dtype, int n_rows, int out_features,
+                               int k_dim, int epilogue, cudaStream_t stream) {
+  if (n_rows <= 0 || out_features <= 0) return IFB_OK;
+  if (k_dim < 8 || k_dim % 8) return IFB_ERR_SIZE;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return IFB_ERR_ALIGN;
+  if (epilogue != 0 && epilogue != 1) return IFB_ERR_ARG;
+  const int nb = n_rows <= 8 ? 1 : n_rows <= 16 ? 2 : n_rows <= 32 ? 4 : 8;
+  if ((n_rows + nb * 8 - 1) / (nb * 8) > 65535) return IFB_ERR_SIZE;
+  if (out_dtype == IFB_BF16)
+    return epilogue ? gv_by_k<1, bf16>(nb, x, w, out, n_rows, out_features, k_dim, stream)
+                    : gv_by_k<0, bf16>(nb, x, w, out, n_rows, out_features, k_dim, stream);
+  if (out_dtype == IFB_F32)
+    return epilogue ? gv_by_k<1, float>(nb, x, w, out, n_rows, out_features, k_dim, stream)
+                    : gv_by_k<0, float>(nb, x, w, out, n_rows, out_features, k_dim, stream);
+  return IFB_ERR_DTYPE;
+}

@@ -18,6 +18,8 @@ linear_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __res
                    int k_dim) {
   __shared__ float xs[TILE_K][TILE_N + 1];
   __shared__ float ws[EPI ? 2 : 1][TILE_K][TILE_O + 1];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   const int tid = threadIdx.x;
   const int tn = tid / 16, to = tid % 16;          // thread's 4x4 patch: rows tn*4.., columns to*4..
   const int n0 = blockIdx.y * TILE_N, o0 = blockIdx.x * TILE_O;
@@ -84,10 +86,8 @@ template <typename TX, typename TW, typename TO>
 static int launch(const void* x, const void* w, void* out, int n, int o, int k, int epi, cudaStream_t s) {
   dim3 grid((o + TILE_O - 1) / TILE_O, (n + TILE_N - 1) / TILE_N);
   if (epi == 0)
-    linear_simt_kernel<TX, TW, TO, 0><<<grid, 256, 0, s>>>((const TX*)x, (const TW*)w, (TO*)out, n, o, k);
-  else
-    linear_simt_kernel<TX, TW, TO, 1><<<grid, 256, 0, s>>>((const TX*)x, (const TW*)w, (TO*)out, n, o, k);
-  return ifb_launch_status();
+    return ifb_launch(linear_simt_kernel<TX, TW, TO, 0>, grid, dim3(256), 0, s, (const TX*)x, (const TW*)w, (TO*)out, n, o, k);
+  return ifb_launch(linear_simt_kernel<TX, TW, TO, 1>, grid, dim3(256), 0, s, (const TX*)x, (const TW*)w, (TO*)out, n, o, k);
 }
 
 // out_features is the width of `out` (for the silu_gate epilogue, half of w's rows).

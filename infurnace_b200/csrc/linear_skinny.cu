@@ -49,6 +49,19 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO*
   const int tile = blockIdx.x, split = blockIdx.y, n0 = blockIdx.z * (NB * 8);
   const int o0 = tile * SK_ROWS + warp * 16;
   const int kb = split * k_per_split, ke = min(k_dim, kb + k_per_split);
+  // the weights are constants: ask L2 for this CTA's slice of them while the kernel before this one
+  // is still finishing, then wait for it (x is its output)
+  {
+    const int row_bytes = (ke - kb) * 2;                                     // bytes of one weight row in this split
+    const int lines = (row_bytes + 127) >> 7;
+    for (int i = tid; i < (EPI ? 2 : 1) * SK_ROWS * lines; i += SK_THREADS) {
+      const int e = i / (SK_ROWS * lines), r = (i / lines) % SK_ROWS, l = i % lines;
+      const int o = min(tile * SK_ROWS + r, o_out - 1);
+      ifb_prefetch_l2(reinterpret_cast<const char*>(w + (size_t)(e * o_out + o) * k_dim + kb) + l * 128);
+    }
+  }
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
   // weight rows of this thread (clamped: rows past the end are computed and dropped)
   const bf16* wrow[NE][2];
 #pragma unroll
@@ -171,9 +184,8 @@ static int sk_launch(const void* x, const void* w, void* out, float* partials, i
     configured = true;
   }
   dim3 grid((o + SK_ROWS - 1) / SK_ROWS, splits, (n + NB * 8 - 1) / (NB * 8));
-  linear_skinny_kernel<NB, EPI, TO><<<grid, SK_THREADS, smem, s>>>((const bf16*)x, (const bf16*)w, (TO*)out, partials,
-                                                                  counters, n, o, k, splits, kps);
-  return ifb_launch_status();
+  return ifb_launch(linear_skinny_kernel<NB, EPI, TO>, grid, dim3(SK_THREADS), smem, s, (const bf16*)x, (const bf16*)w,
+                    (TO*)out, partials, counters, n, o, k, splits, kps);
 }
 
 template <int EPI, typename TO>

@@ -29,7 +29,7 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"
 
 # library name -> (sources, extra flags)
 LIBRARIES: Dict[str, tuple] = {
-    "core": (["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "linear_skinny.cu"], []),
+    "core": (["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "linear_skinny.cu", "linear_gemv.cu"], []),
     "linear_tcgen05": (["linear_tcgen05.cu"], []),
     # the few-rows product with its scratch inside the library, for callers that must not allocate
     "linear_skinny_static": (["linear_skinny_static.cu"], []),

@@ -72,10 +72,12 @@ class CudaKernels:
                                       c_void_p]
         c.ifb_linear_skinny.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p]
+        c.ifb_linear_gemv.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         c.ifb_linear_skinny_scratch.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
         c.ifb_linear_skinny_scratch.restype = None
         self._lin_partials = None
         self._lin_counters = None
+        self.gemv_max_rows = 64        # up to here: the kernel without global partial sums
         self.skinny_max_rows = 4096    # above this the plain kernel runs (until a large-tile kernel takes over)
         self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
         self._tc_err = None            # device int: non-zero after a bounded wait in a tcgen05 kernel gave up
@@ -143,6 +145,8 @@ class CudaKernels:
                 and out.dtype in (torch.bfloat16, torch.float32):
             if n >= self.tc_min_rows:
                 return self._linear_tcgen05(x, w, out, n, o, k, epi)
+            if n <= self.gemv_max_rows:
+                return self._linear_gemv(x, w, out, n, o, k, epi)
             return self._linear_skinny(x, w, out, n, o, k, epi)
         self.launches += 1
         _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
@@ -168,6 +172,11 @@ class CudaKernels:
                 self._tc_err.zero_()
                 raise KernelError(f"a tcgen05 product gave up waiting on a barrier (code {code}: 1 producer, 2 issuer, "
                                   "3 epilogue); its output is not valid")
+
+    def _linear_gemv(self, x, w, out, n, o, k, epi):
+        self.launches += 1
+        _check(self.core.ifb_linear_gemv(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), n, o, k, epi,
+                                         self._stream()), "linear")
 
     def linear_splits(self, n, o, k):
         """CTAs that share the k range of one 64-feature tile: enough to cover the SMs twice, and

@@ -263,3 +263,21 @@ def test_linear_tcgen05(K, od, n, o, k, epilogue):
     K.check_device_errors()
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2 if od == torch.bfloat16 else 2e-4,
                                atol=2e-3 if od == torch.bfloat16 else 1e-4)
+
+
+@pytest.mark.parametrize("od", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,o,k", [(1, 72, 72), (8, 4096, 1024), (3, 1000, 3072), (16, 333, 136), (17, 64, 1024),
+                                   (64, 1024, 2048), (33, 200, 1000), (1, 151936, 1024), (9, 17, 8)])
+@pytest.mark.parametrize("epilogue", ["none", "silu_gate"])
+def test_linear_gemv(K, od, n, o, k, epilogue):
+    """The few-rows product whose warps split k inside the CTA (no partial sums in global memory)."""
+    if o > 100000 and epilogue != "none":
+        pytest.skip("one large case is enough")
+    x = rnd((n, k), torch.bfloat16, 4)
+    w = rnd((2 * o if epilogue == "silu_gate" else o, k), torch.bfloat16, 5, scale=k ** -0.5)
+    ref = torch.empty((n, o), dtype=od)
+    REF.linear(x, w, ref, epilogue)
+    out = torch.full((n, o), float("nan"), dtype=od, device="cuda")
+    K._linear_gemv(x.cuda(), w.cuda(), out, n, o, k, 1 if epilogue == "silu_gate" else 0)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2 if od == torch.bfloat16 else 2e-4,
+                               atol=2e-3 if od == torch.bfloat16 else 1e-4)
