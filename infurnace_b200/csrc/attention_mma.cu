@@ -55,6 +55,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware approximation (relative error about 2^-22, far below bfloat16's and the softmax's needs);
+// -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -136,23 +143,26 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KB][4], const bf1
   mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
   const float mA = fmaxf(m[0], mxA), mB = fmaxf(m[1], mxB);
   const float uA = mA == -INFINITY ? 0.f : mA, uB = mB == -INFINITY ? 0.f : mB;   // all keys masked so far
-  const float cA = exp2f(m[0] - uA), cB = exp2f(m[1] - uB);
+  const float cA = fast_exp2(m[0] - uA), cB = fast_exp2(m[1] - uB);
+  const bool moved = (mA != m[0]) || (mB != m[1]);          // did a running maximum rise in this tile?
   m[0] = mA; m[1] = mB;
   float sumA = 0.f, sumB = 0.f;
 #pragma unroll
   for (int j = 0; j < NB; ++j) {
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      s[j][e] = exp2f(s[j][e] - uA);
-      s[j][2 + e] = exp2f(s[j][2 + e] - uB);
+      s[j][e] = fast_exp2(s[j][e] - uA);
+      s[j][2 + e] = fast_exp2(s[j][2 + e] - uB);
       sumA += s[j][e];
       sumB += s[j][2 + e];
     }
   }
   l[0] = l[0] * cA + sumA;   // per-thread partial of the row's denominator; summed over the quad at the end
   l[1] = l[1] * cB + sumB;
+  if (__any_sync(0xffffffffu, moved)) {                     // else both factors are exactly 1 for every lane
 #pragma unroll
-  for (int n = 0; n < D / 8; ++n) { o[n][0] *= cA; o[n][1] *= cA; o[n][2] *= cB; o[n][3] *= cB; }
+    for (int n = 0; n < D / 8; ++n) { o[n][0] *= cA; o[n][1] *= cA; o[n][2] *= cB; o[n][3] *= cB; }
+  }
   // o += p v
 #pragma unroll
   for (int kk = 0; kk < NB / 2; ++kk) {
@@ -191,9 +201,10 @@ __global__ void __launch_bounds__(THREADS)
 attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __restrict__ pages,
                     const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                     const int* __restrict__ seq_lens, bf16* __restrict__ out, float* __restrict__ part_o,
-                    float* __restrict__ part_ml, int nq, int nkv, int page_size, float scale_log2, int window,
-                    int num_splits) {
+                    float* __restrict__ part_ml, int* __restrict__ counters, int nq, int nkv, int page_size,
+                    float scale_log2, int window, int num_splits) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int is_last;
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][DP]
   bf16* KV = Qs + 16 * DP;                                   // SQ_STAGES x (K [BN][DP], V [BN][DP])
   ifb_pdl_wait();
@@ -304,33 +315,33 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
       if (dim == 0) { part_ml[base * 2] = M; part_ml[base * 2 + 1] = den; }
     }
   }
-}
-
-// merge of the splits: one warp per (token, query head) of the requests the small-q kernel took
-__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                  const int* __restrict__ cu_q, bf16* __restrict__ out, int n_tokens, int n_req, int nq,
-                                  int nkv, int num_splits) {
-  ifb_pdl_wait();
-  ifb_pdl_trigger();
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= n_tokens * nq) return;
-  const int tok = warp / nq;
-  if (tok >= cu_q[n_req]) return;
-  int lo = 0, hi = n_req;
-  while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (cu_q[mid] <= tok) lo = mid; else hi = mid; }
-  if ((cu_q[lo + 1] - cu_q[lo]) * (nq / nkv) > 16) return;
-  const size_t base = (size_t)warp * num_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  const float U = M == -INFINITY ? 0.f : M;
-  float den = 0.f;
-  for (int s = 0; s < num_splits; ++s) den += part_ml[(base + s) * 2 + 1] * exp2f(part_ml[(base + s) * 2] - U);
-  const float inv = den > 0.f ? 1.f / den : 0.f;
-  for (int dim = lane; dim < D; dim += 32) {
-    float acc = 0.f;
-    for (int s = 0; s < num_splits; ++s) acc += part_o[(base + s) * D + dim] * exp2f(part_ml[(base + s) * 2] - U);
-    out[(size_t)warp * D + dim] = __float2bfloat16_rn(acc * inv);
+  if (num_splits == 1) return;
+  // the CTA that finishes last for this (request, key/value head) merges the splits, in split order
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&counters[r * nkv + kvh], 1);
+    is_last = (old == num_splits - 1);
   }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = tid; idx < rows * D; idx += THREADS) {
+    const int row = idx / D, dim = idx % D;
+    const int tok = q0 + row / G, head = kvh * G + row % G;
+    const size_t base = ((size_t)tok * nq + head) * num_splits;
+    float M = -INFINITY;
+    for (int sp = 0; sp < num_splits; ++sp) M = fmaxf(M, part_ml[(base + sp) * 2]);
+    const float U = M == -INFINITY ? 0.f : M;
+    float den = 0.f, acc = 0.f;
+    for (int sp = 0; sp < num_splits; ++sp) {
+      const float f = exp2f(part_ml[(base + sp) * 2] - U);
+      den += part_ml[(base + sp) * 2 + 1] * f;
+      acc += part_o[(base + sp) * D + dim] * f;
+    }
+    out[((size_t)tok * nq + head) * D + dim] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+  }
+  if (tid == 0) counters[r * nkv + kvh] = 0;       // ready for the next launch
 }
 
 // --------------------------------------------------------------------------------------------
@@ -438,7 +449,7 @@ IFB_EXPORT long long ifb_attention_mma_scratch_floats(int n_tokens, int nq, int 
 // tiles: launch the tile kernel.  Requests are routed by rows = q_len * (nq / nkv) <= 16.
 IFB_EXPORT int ifb_attention_mma(const void* qkv, int row_stride, const void* pages, const int* block_tables,
                                  int bt_stride, const int* cu_q, const int* seq_lens, void* out, float* scratch,
-                                 int n_tokens, int n_req, int nq, int nkv, int d, int page_size, float scale,
+                                 int* counters, int n_tokens, int n_req, int nq, int nkv, int d, int page_size, float scale,
                                  int window, int max_q_len, int num_splits, int run_small, int run_tiles,
                                  cudaStream_t stream) {
   if (n_tokens <= 0 || n_req <= 0) return IFB_OK;
@@ -457,20 +468,14 @@ IFB_EXPORT int ifb_attention_mma(const void* qkv, int row_stride, const void* pa
   }
   const float scale_log2 = scale * 1.4426950408889634f;
   if (run_small) {
-    if (num_splits > 1 && !scratch) return IFB_ERR_ARG;
+    if (num_splits > 1 && (!scratch || !counters)) return IFB_ERR_ARG;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_tokens * nq * num_splits * D : nullptr;
     dim3 grid(num_splits, nkv, n_req);
     int st = ifb_launch(attn_small_q_kernel, grid, dim3(THREADS), small_q_smem(), stream, (const bf16*)qkv, row_stride,
-                        (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, part_o, part_ml, nq, nkv,
-                        page_size, scale_log2, window, num_splits);
+                        (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, part_o, part_ml, counters,
+                        nq, nkv, page_size, scale_log2, window, num_splits);
     if (st) return st;
-    if (num_splits > 1) {
-      const long long warps = (long long)n_tokens * nq;
-      st = ifb_launch(attn_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
-                      (const float*)part_ml, cu_q, (bf16*)out, n_tokens, n_req, nq, nkv, num_splits);
-      if (st) return st;
-    }
   }
   if (run_tiles) {
     const int tpc = 4 * (16 / G);

@@ -187,7 +187,22 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, const
   // the largest value and its lowest index; the row is walked with consecutive threads on consecutive
   // elements (any partition gives the same answer, since ties go to the lower index)
   float bv = -INFINITY; int bi = 0x7fffffff;
-  for (int i = tid; i < vocab; i += nthreads) { const float v = l[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+  if ((((uintptr_t)l) & 15) == 0) {      // 16-byte loads, four in flight per thread
+    const int v4 = vocab >> 2;
+    const float4* l4 = reinterpret_cast<const float4*>(l);
+#pragma unroll 4
+    for (int i = tid; i < v4; i += nthreads) {
+      const float4 v = l4[i];
+      const int b = i << 2;
+      if (v.x > bv || (v.x == bv && b < bi)) { bv = v.x; bi = b; }
+      if (v.y > bv || (v.y == bv && b + 1 < bi)) { bv = v.y; bi = b + 1; }
+      if (v.z > bv || (v.z == bv && b + 2 < bi)) { bv = v.z; bi = b + 2; }
+      if (v.w > bv || (v.w == bv && b + 3 < bi)) { bv = v.w; bi = b + 3; }
+    }
+    for (int i = (v4 << 2) + tid; i < vocab; i += nthreads) { const float v = l[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+  } else {
+    for (int i = tid; i < vocab; i += nthreads) { const float v = l[i]; if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+  }
   for (int o = 16; o > 0; o >>= 1) {
     float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
     if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }

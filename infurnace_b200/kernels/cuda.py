@@ -85,6 +85,7 @@ class CudaKernels:
         self.tc_min_rows = 65
         self._attn_mma = {}        # head size -> library
         self._attn_scratch = None
+        self._attn_counters = None
         self.sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self.attention_scratch_cap = 64 << 20     # bytes of split scratch beyond which a step runs unsplit
         c.ifb_paged_attention_simt.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -266,8 +267,8 @@ class CudaKernels:
         if lib is None:
             lib = load_library("attention_mma", {"HEAD_DIM": head_dim}, progress=self._progress)
             lib.ifb_attention_mma.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                              c_int, c_int, c_int, c_void_p]
+                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                              c_int, c_int, c_int, c_int, c_void_p]
             lib.ifb_attention_mma_scratch_floats.restype = c_longlong
             lib.ifb_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int]
             self._attn_mma[head_dim] = lib
@@ -276,10 +277,10 @@ class CudaKernels:
     def attention_splits(self, num_requests, num_kv_heads, max_seq_len, window=0):
         """How many CTAs share one (request, key/value head) of the small-q kernel: as many as
         keep the whole grid resident at once (two CTAs fit on an SM), so that no second wave
-        runs, and no fewer than 256 keys per split."""
+        runs, and no fewer than 128 keys (two tiles) per split."""
         reach = min(max_seq_len, window + 16) if window else max_seq_len
         fit = (2 * self.sm_count) // max(1, num_requests * num_kv_heads)
-        return max(1, min(fit, -(-reach // 256), 32))
+        return max(1, min(fit, -(-reach // 128), 32))
 
     def attention_scratch(self, floats):
         if self._attn_scratch is None or self._attn_scratch.numel() < floats:
@@ -298,10 +299,16 @@ class CudaKernels:
         if need * 4 > self.attention_scratch_cap:
             num_splits, need = 1, 0
         scratch = self.attention_scratch(need) if need else None
-        self.launches += (2 if num_splits > 1 else 1) + (0 if only_small else 1)
+        counters = None
+        if need:
+            if self._attn_counters is None or self._attn_counters.numel() < r * num_kv_heads:
+                self._attn_counters = torch.zeros(max(r * num_kv_heads, 4096), dtype=torch.int32, device="cuda")
+                self.scratch_generation += 1
+            counters = self._attn_counters
+        self.launches += 1 + (0 if only_small else 1)
         _check(lib.ifb_attention_mma(
             qkv.data_ptr(), qkv.stride(0), kv_pages.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
-            cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), _ptr(scratch), n, r, num_heads, num_kv_heads,
+            cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), _ptr(scratch), _ptr(counters), n, r, num_heads, num_kv_heads,
             head_dim, kv_pages.shape[3], float(scale), int(window), int(max_q_len), int(num_splits), 1,
             0 if only_small else 1, self._stream()), "paged_attention")
 
