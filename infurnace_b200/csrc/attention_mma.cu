@@ -16,8 +16,20 @@
 // Both read every key, this step's own included, from the pages named by the request's block
 // table: the query at position p sees positions max(0, p-window+1) .. p.  Keys outside what a
 // CTA needs are not fetched (block-table entries of pages that a window has passed are stale).
+//
+// How a tile of keys and values reaches shared memory.  With head sizes that are multiples of 64 and
+// pages of 16, 32 or 64 tokens, TMA brings it: the page pool is described by one tensor map as a
+// matrix [pages * 2 * kv_heads * page_size, head_dim], a page's keys (or values) of one head are one
+// box per 64 columns, written in the 128-byte swizzle, which ldmatrix then reads without bank
+// conflicts.  Sixteen lanes of warp 0 issue a tile's boxes; a stage's mbarrier counts the bytes.  A
+// page that lies outside the keys a CTA needs is fetched from a row beyond the tensor (zeros).  Waits
+// on the barriers are bounded: after ATT_SPIN_LIMIT polls a thread records a code in `*err`, raises
+// the CTA's abort flag and the CTA leaves.  Other sizes take the cp.async path: 16-byte copies by all
+// threads into padded rows.
 #include "common.cuh"
+#include <cuda.h>
 #include <math.h>
+#include <string.h>
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<head size>"
@@ -34,6 +46,9 @@ constexpr int THREADS = 128;
 constexpr int KCH = D / 8;         // 16-byte pieces of a row
 constexpr int KB = D / 16;         // k-blocks of a q.k product, n-block pairs of a p.v product
 constexpr int SQ_STAGES = 3;       // tile buffers of the small-q kernel: two tiles are in flight while one is used
+constexpr bool TMA_D = (D % 64 == 0);            // head sizes the TMA path takes
+constexpr int HALVES = TMA_D ? D / 64 : 1;       // 64-column (128-byte) boxes per row
+constexpr uint32_t ATT_SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -67,6 +82,59 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ void att_mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void att_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool att_mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  False: gave up (the abort flag is up and *err holds `code`).
+__device__ __forceinline__ bool att_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+  for (uint32_t i = 0; i < ATT_SPIN_LIMIT; ++i) {
+    if (att_mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(err, code);
+  return false;
+}
+__device__ __forceinline__ void att_tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Address of 8 elements (key, col .. col+7) of a K or V tile.  Padded layout: [BN][DP].  Swizzled layout (what
+// TMA wrote): [HALVES][BN][64], the 16-byte piece c of a row stored at c ^ (row & 7); the tile is 1024-byte aligned.
+template <bool SWZ>
+__device__ __forceinline__ const bf16* kv_at(const bf16* tile, int key, int col) {
+  if (SWZ) return tile + (col >> 6) * (BN * 64) + key * 64 + ((((col & 63) >> 3) ^ (key & 7)) << 3);
+  return tile + key * DP + col;
+}
+
+// One tile by TMA, issued by warp 0 (all 32 lanes call): K to `stage`, V to `stage + BN*D`.  Pages that do not
+// overlap the keys [k_lo, k_hi] are read from beyond the tensor's last row, which gives zeros.
+__device__ __forceinline__ void tma_issue_tile(const CUtensorMap* map, bf16* stage, uint64_t* bar, const int* __restrict__ bt,
+                                               int tile_key0, int k_lo, int k_hi, int kvh, int nkv, int page_size,
+                                               int ps_shift, int total_rows, int lane) {
+  const int ppt = BN >> ps_shift;                    // pages per tile
+  const int n_ops = ppt * HALVES * 2;                // at most 4 * 4 * 2 = 32
+  if (lane == 0) att_mbar_expect_tx(bar, 2u * BN * D * sizeof(bf16));
+  __syncwarp();
+  if (lane < n_ops) {
+    const int kv = lane / (ppt * HALVES), rem = lane % (ppt * HALVES), pg = rem / HALVES, half = rem % HALVES;
+    const int key0 = tile_key0 + pg * page_size;
+    int y = total_rows;
+    if (key0 <= k_hi && key0 + page_size - 1 >= k_lo) y = ((bt[key0 >> ps_shift] * 2 + kv) * nkv + kvh) * page_size;
+    att_tma_load_2d(stage + kv * (BN * D) + half * (BN * 64) + pg * page_size * 64, map, bar, half * 64, y);
+  }
+}
+
 // Keys key0 .. key0+BN-1 of one key/value head into Ks and Vs ([BN][DP]); keys outside [lo, hi] are zeros.
 // Consecutive threads copy consecutive 16-byte pieces of a row, so a warp's copy instruction covers whole
 // 128-byte lines (a piece per thread at scattered rows would cost a memory request each).
@@ -98,7 +166,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
 // One warp: scores of its 16 query rows (fragments qf) against keys [kbeg, kbeg + 8*NB) of the tile in
 // Ks/Vs, masking, online softmax update of (m, l, o).  Row A of a thread is lane/4, row B is that + 8.
 // pA/pB: position of the row's query (-1000000000: the row does not exist); wlo: window (0: none).
-template <int NB, bool MASK>
+template <int NB, bool MASK, bool SWZ>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KB][4], const bf16* Ks, const bf16* Vs, int kbeg,
                                           int key0, int klo, int khi, int pA, int pB, int window, float scale_log2,
                                           float (&m)[2], float (&l)[2], float (&o)[D / 8][4], int lane) {
@@ -112,7 +180,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KB][4], const bf1
       uint32_t b[4];
       const int key = kbeg + j * 8 + (lane & 7) + ((lane >> 4) << 3);
       const int col = kb * 16 + (((lane >> 3) & 1) << 3);
-      ldmatrix_x4(b, Ks + key * DP + col);
+      ldmatrix_x4(b, kv_at<SWZ>(Ks, key, col));
       mma_bf16(s[j], qf[kb], b[0], b[1]);
       mma_bf16(s[j + 1], qf[kb], b[2], b[3]);
     }
@@ -176,7 +244,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KB][4], const bf1
       uint32_t b[4];
       const int key = kbeg + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
       const int col = n2 * 16 + ((lane >> 4) << 3);
-      ldmatrix_x4_trans(b, Vs + key * DP + col);
+      ldmatrix_x4_trans(b, kv_at<SWZ>(Vs, key, col));
       mma_bf16(o[2 * n2], a, b[0], b[1]);
       mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
     }
@@ -197,16 +265,24 @@ constexpr int NO_ROW = -1000000000;
 // --------------------------------------------------------------------------------------------
 // small-q kernel: grid (num_splits, kv heads, requests)
 // --------------------------------------------------------------------------------------------
+template <bool TMA>
 __global__ void __launch_bounds__(THREADS)
-attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __restrict__ pages,
+attn_small_q_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, int* __restrict__ err,
+                    const bf16* __restrict__ qkv, int row_stride, const bf16* __restrict__ pages,
                     const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                     const int* __restrict__ seq_lens, bf16* __restrict__ out, float* __restrict__ part_o,
                     float* __restrict__ part_ml, int* __restrict__ counters, int nq, int nkv, int page_size,
                     float scale_log2, int window, int num_splits) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int is_last;
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [16][DP]
-  bf16* KV = Qs + 16 * DP;                                   // SQ_STAGES x (K [BN][DP], V [BN][DP])
+  __shared__ uint64_t full_bar[SQ_STAGES];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  constexpr int STAGE = TMA ? 2 * BN * D : 2 * BN * DP;       // elements of one stage: K tile then V tile
+  // the stages first (TMA wants them 1024-byte aligned), then the 16 query rows
+  const uint32_t raw = smem_u32(smem_raw);
+  bf16* KV = reinterpret_cast<bf16*>(smem_raw + (TMA ? ((raw + 1023u) & ~1023u) - raw : 0u));
+  bf16* Qs = KV + SQ_STAGES * STAGE;                          // [16][DP]
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
@@ -221,9 +297,21 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
   int per = total > 0 ? (total + num_splits - 1) / num_splits : 0;
   per = (per + BN - 1) / BN * BN;
   const int k_begin = lo + split * per, k_end = min(hi + 1, k_begin + per);
-  const int n_tiles = k_end > k_begin ? (k_end - k_begin + BN - 1) / BN : 0;
+  // tiles start at multiples of BN keys with TMA (a box is a whole page), else at the first key
+  const int T0 = TMA ? (k_begin / BN) * BN : k_begin;
+  const int n_tiles = k_end > k_begin ? (k_end - T0 + BN - 1) / BN : 0;
   const int* bt = block_tables + (size_t)r * bt_stride;
+  const int ps_shift = __ffs(page_size) - 1;                  // TMA path: page_size is a power of two
 
+  if (TMA) {
+    if (tid == 0) {
+      for (int st = 0; st < SQ_STAGES; ++st) att_mbar_init(&full_bar[st], 1);
+      abort_word = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    __syncthreads();
+  }
   // the query rows: row = token * G + head-in-group
   for (int c = tid; c < 16 * KCH; c += THREADS) {
     const int row = c / KCH, ch = c % KCH;
@@ -231,14 +319,21 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
     const bf16* src = valid ? qkv + (size_t)(q0 + row / G) * row_stride + (size_t)(kvh * G + row % G) * D + ch * 8 : qkv;
     cp_async16(Qs + row * DP + ch * 8, src, valid);
   }
-  // prologue: tiles 0 .. SQ_STAGES-2 in flight (one commit group per tile, empty groups past the end)
+  cp_async_commit();
+  // prologue: tiles 0 .. SQ_STAGES-2 in flight
 #pragma unroll
   for (int st = 0; st < SQ_STAGES - 1; ++st) {
     if (st < n_tiles) {
-      bf16* Kn = KV + st * 2 * BN * DP;
-      load_kv_tile(Kn, Kn + BN * DP, pages, bt, k_begin + st * BN, k_begin, k_end - 1, kvh, nkv, page_size, tid);
+      bf16* Kn = KV + st * STAGE;
+      if (TMA) {
+        if (warp == 0)
+          tma_issue_tile(&kv_map, Kn, &full_bar[st], bt, T0 + st * BN, k_begin, k_end - 1, kvh, nkv, page_size, ps_shift,
+                         total_rows, lane);
+      } else {
+        load_kv_tile(Kn, Kn + BN * DP, pages, bt, T0 + st * BN, k_begin, k_end - 1, kvh, nkv, page_size, tid);
+      }
     }
-    cp_async_commit();
+    if (!TMA) cp_async_commit();
   }
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -248,29 +343,46 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
   const int rowA = lane >> 2, rowB = rowA + 8;
   const int pA = rowA < rows ? p_first + rowA / G : NO_ROW, pB = rowB < rows ? p_first + rowB / G : NO_ROW;
   uint32_t qf[KB][4];
+  bool ok = true;
   for (int t = 0; t < n_tiles; ++t) {
     const int stage = t % SQ_STAGES;
-    bf16* Ks = KV + stage * 2 * BN * DP;
-    bf16* Vs = Ks + BN * DP;
-    cp_async_wait<SQ_STAGES - 2>();          // tile t has landed (for this thread's copies)
+    bf16* Ks = KV + stage * STAGE;
+    bf16* Vs = Ks + (TMA ? BN * D : BN * DP);
+    if (TMA) {
+      if (t == 0) cp_async_wait<0>();        // the query rows
+      ok = att_mbar_wait(&full_bar[stage], (t / SQ_STAGES) & 1, abort_flag, err, 1);
+    } else {
+      cp_async_wait<SQ_STAGES - 2>();        // tile t has landed (for this thread's copies)
+    }
     __syncthreads();                         // ... for everyone's; and everyone is done with tile t-1
+    if (TMA && *abort_flag) { ok = false; break; }
     const int nt = t + SQ_STAGES - 1;        // refill the stage that tile t-1 used
     if (nt < n_tiles) {
-      bf16* Kn = KV + (nt % SQ_STAGES) * 2 * BN * DP;
-      load_kv_tile(Kn, Kn + BN * DP, pages, bt, k_begin + nt * BN, k_begin, k_end - 1, kvh, nkv, page_size, tid);
+      bf16* Kn = KV + (nt % SQ_STAGES) * STAGE;
+      if (TMA) {
+        if (warp == 0)
+          tma_issue_tile(&kv_map, Kn, &full_bar[nt % SQ_STAGES], bt, T0 + nt * BN, k_begin, k_end - 1, kvh, nkv, page_size,
+                         ps_shift, total_rows, lane);
+      } else {
+        load_kv_tile(Kn, Kn + BN * DP, pages, bt, T0 + nt * BN, k_begin, k_end - 1, kvh, nkv, page_size, tid);
+      }
     }
-    cp_async_commit();
+    if (!TMA) cp_async_commit();
     if (t == 0) load_q_frags(qf, Qs, lane);
     // a tile every key of which every existing row sees needs no masking (rows that do not exist have
     // zero queries and are never written)
-    const int tile0 = k_begin + t * BN;
-    const bool interior = tile0 + BN - 1 <= min(p_first, k_end - 1) && (window == 0 || tile0 >= L - window);
+    const int tile0 = T0 + t * BN;
+    const bool interior = tile0 >= k_begin && tile0 + BN - 1 <= min(p_first, k_end - 1) && (window == 0 || tile0 >= L - window);
     if (interior)
-      warp_tile<2, false>(qf, Ks, Vs, warp * 16, tile0, k_begin, k_end - 1, pA, pB, window, scale_log2, m, l, o, lane);
+      warp_tile<2, false, TMA>(qf, Ks, Vs, warp * 16, tile0, k_begin, k_end - 1, pA, pB, window, scale_log2, m, l, o, lane);
     else
-      warp_tile<2, true>(qf, Ks, Vs, warp * 16, tile0, k_begin, k_end - 1, pA, pB, window, scale_log2, m, l, o, lane);
+      warp_tile<2, true, TMA>(qf, Ks, Vs, warp * 16, tile0, k_begin, k_end - 1, pA, pB, window, scale_log2, m, l, o, lane);
   }
   cp_async_wait<0>();
+  if (TMA && !ok) {                          // a wait gave up: let copies in flight land, then leave
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    return;
+  }
   __syncthreads();
   // merge the four warps' (m, l, o) through shared memory (the tile buffers are free now)
   float* sm_o = reinterpret_cast<float*>(KV);                // [4][16][D]
@@ -347,14 +459,21 @@ attn_small_q_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __
 // --------------------------------------------------------------------------------------------
 // tile kernel: grid (query tiles, kv heads, requests); a warp keeps floor(16/G) tokens x G heads
 // --------------------------------------------------------------------------------------------
+template <bool TMA>
 __global__ void __launch_bounds__(THREADS)
-attn_tile_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __restrict__ pages,
+attn_tile_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, int* __restrict__ err,
+                 const bf16* __restrict__ qkv, int row_stride, const bf16* __restrict__ pages,
                  const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                  const int* __restrict__ seq_lens, bf16* __restrict__ out, int nq, int nkv, int page_size,
                  float scale_log2, int window) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [64][DP]
-  bf16* KV = Qs + 64 * DP;
+  __shared__ uint64_t full_bar[2];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  constexpr int STAGE = TMA ? 2 * BN * D : 2 * BN * DP;
+  const uint32_t raw = smem_u32(smem_raw);
+  bf16* KV = reinterpret_cast<bf16*>(smem_raw + (TMA ? ((raw + 1023u) & ~1023u) - raw : 0u));
+  bf16* Qs = KV + 2 * STAGE;                                 // [64][DP]
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int kvh = blockIdx.y, r = blockIdx.z;
@@ -368,8 +487,20 @@ attn_tile_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __res
   const int t1 = min(q_len, t0 + tpc);
   const int p_first = L - q_len;
   const int lo = window > 0 ? max(0, p_first + t0 - window + 1) : 0, hi = p_first + t1 - 1;
-  const int n_tiles = hi >= lo ? (hi + 1 - lo + BN - 1) / BN : 0;
+  const int T0 = TMA ? (lo / BN) * BN : lo;
+  const int n_tiles = hi >= lo ? (hi + 1 - T0 + BN - 1) / BN : 0;
   const int* bt = block_tables + (size_t)r * bt_stride;
+  const int ps_shift = __ffs(page_size) - 1;
+  if (TMA) {
+    if (tid == 0) {
+      att_mbar_init(&full_bar[0], 1);
+      att_mbar_init(&full_bar[1], 1);
+      abort_word = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    __syncthreads();
+  }
   for (int c = tid; c < 64 * KCH; c += THREADS) {
     const int row = c / KCH, ch = c % KCH;
     const int w = row >> 4, rr = row & 15;
@@ -378,8 +509,15 @@ attn_tile_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __res
     const bf16* src = valid ? qkv + (size_t)(q0 + tok) * row_stride + (size_t)(kvh * G + rr % G) * D + ch * 8 : qkv;
     cp_async16(Qs + row * DP + ch * 8, src, valid);
   }
-  if (n_tiles > 0) load_kv_tile(KV, KV + BN * DP, pages, bt, lo, lo, hi, kvh, nkv, page_size, tid);
   cp_async_commit();
+  if (n_tiles > 0) {
+    if (TMA) {
+      if (warp == 0) tma_issue_tile(&kv_map, KV, &full_bar[0], bt, T0, lo, hi, kvh, nkv, page_size, ps_shift, total_rows, lane);
+    } else {
+      load_kv_tile(KV, KV + BN * DP, pages, bt, T0, lo, hi, kvh, nkv, page_size, tid);
+    }
+  }
+  if (!TMA) cp_async_commit();
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[D / 8][4];
 #pragma unroll
@@ -390,30 +528,46 @@ attn_tile_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __res
   const int pB = (rowB < tpw * G && tokB < t1) ? p_first + tokB : NO_ROW;
   const int warp_hi = p_first + min(t1, t0 + (warp + 1) * tpw) - 1;        // last position this warp's rows see
   uint32_t qf[KB][4];
+  bool ok = true;
   for (int t = 0; t < n_tiles; ++t) {
-    bf16* Ks = KV + (t & 1) * 2 * BN * DP;
-    bf16* Vs = Ks + BN * DP;
+    bf16* Ks = KV + (t & 1) * STAGE;
+    bf16* Vs = Ks + (TMA ? BN * D : BN * DP);
+    // tile t+1 goes to the other stage, which every warp left at the barrier that ended iteration t-1
     if (t + 1 < n_tiles) {
-      bf16* Kn = KV + ((t + 1) & 1) * 2 * BN * DP;
-      load_kv_tile(Kn, Kn + BN * DP, pages, bt, lo + (t + 1) * BN, lo, hi, kvh, nkv, page_size, tid);
-      cp_async_commit();
-      cp_async_wait<1>();
+      bf16* Kn = KV + ((t + 1) & 1) * STAGE;
+      if (TMA) {
+        if (warp == 0)
+          tma_issue_tile(&kv_map, Kn, &full_bar[(t + 1) & 1], bt, T0 + (t + 1) * BN, lo, hi, kvh, nkv, page_size, ps_shift,
+                         total_rows, lane);
+      } else {
+        load_kv_tile(Kn, Kn + BN * DP, pages, bt, T0 + (t + 1) * BN, lo, hi, kvh, nkv, page_size, tid);
+        cp_async_commit();
+      }
+    }
+    if (TMA) {
+      if (t == 0) cp_async_wait<0>();
+      ok = att_mbar_wait(&full_bar[t & 1], (t >> 1) & 1, abort_flag, err, 2);
     } else {
-      cp_async_wait<0>();
+      if (t + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
     }
     __syncthreads();
+    if (TMA && *abort_flag) { ok = false; break; }
     if (t == 0) load_q_frags(qf, Qs + warp * 16 * DP, lane);
-    const int tile0 = lo + t * BN;
+    const int tile0 = T0 + t * BN;
     if (tile0 <= warp_hi) {
       // every key of the tile is seen by every row of this warp: no masking
       const bool interior = t0 + warp * tpw < t1 && tile0 >= lo && tile0 + BN - 1 <= min(hi, p_first + t0 + warp * tpw) &&
                             (window == 0 || tile0 >= warp_hi - window + 1);
       if (interior)
-        warp_tile<8, false>(qf, Ks, Vs, 0, tile0, lo, hi, pA, pB, window, scale_log2, m, l, o, lane);
+        warp_tile<8, false, TMA>(qf, Ks, Vs, 0, tile0, lo, hi, pA, pB, window, scale_log2, m, l, o, lane);
       else
-        warp_tile<8, true>(qf, Ks, Vs, 0, tile0, lo, hi, pA, pB, window, scale_log2, m, l, o, lane);
+        warp_tile<8, true, TMA>(qf, Ks, Vs, 0, tile0, lo, hi, pA, pB, window, scale_log2, m, l, o, lane);
     }
     __syncthreads();
+  }
+  if (TMA && !ok) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    return;
   }
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
@@ -435,8 +589,46 @@ attn_tile_kernel(const bf16* __restrict__ qkv, int row_stride, const bf16* __res
   }
 }
 
-static size_t small_q_smem() { return (size_t)(16 * DP + SQ_STAGES * 2 * BN * DP) * sizeof(bf16); }
-static size_t tile_smem() { return (size_t)(64 * DP + 4 * BN * DP) * sizeof(bf16); }
+// ---------------------------------------------------------------------------------------------------
+static size_t small_q_smem(bool tma) {
+  return tma ? (size_t)(SQ_STAGES * 2 * BN * D + 16 * DP) * sizeof(bf16) + 1024 : (size_t)(SQ_STAGES * 2 * BN * DP + 16 * DP) * sizeof(bf16);
+}
+static size_t tile_smem(bool tma) {
+  return tma ? (size_t)(2 * 2 * BN * D + 64 * DP) * sizeof(bf16) + 1024 : (size_t)(2 * 2 * BN * DP + 64 * DP) * sizeof(bf16);
+}
+
+typedef CUresult (*AttEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The pool [pages, 2, kv_heads, page_size, D] as a matrix [rows, D] with boxes of page_size rows x 64 columns in
+// the 128-byte swizzle.  Maps are kept by (address, rows, page size): a model has one pool per layer.
+static int kv_tensor_map(CUtensorMap* out, const void* pages, long long rows, int page_size) {
+  struct Entry { const void* p; long long rows; int ps; CUtensorMap map; };
+  static Entry cache[512];
+  static int used = 0;
+  for (int i = 0; i < used; ++i)
+    if (cache[i].p == pages && cache[i].rows == rows && cache[i].ps == page_size) { *out = cache[i].map; return IFB_OK; }
+  static AttEncodeTiledFn enc = nullptr;
+  if (!enc) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return IFB_ERR_ARG;
+    enc = (AttEncodeTiledFn)fn;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(bf16)};
+  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return IFB_ERR_ARG;
+  if (used < 512) { cache[used].p = pages; cache[used].rows = rows; cache[used].ps = page_size; cache[used].map = m; ++used; }
+  *out = m;
+  return IFB_OK;
+}
 
 IFB_EXPORT int ifb_attention_mma_head_dim() { return D; }
 
@@ -445,13 +637,46 @@ IFB_EXPORT long long ifb_attention_mma_scratch_floats(int n_tokens, int nq, int 
   return num_splits > 1 ? (long long)n_tokens * nq * num_splits * (D + 2) : 0;
 }
 
-// max_q_len: the most query tokens any request brings.  small: launch the small-q kernel (and the merge);
-// tiles: launch the tile kernel.  Requests are routed by rows = q_len * (nq / nkv) <= 16.
-IFB_EXPORT int ifb_attention_mma(const void* qkv, int row_stride, const void* pages, const int* block_tables,
-                                 int bt_stride, const int* cu_q, const int* seq_lens, void* out, float* scratch,
-                                 int* counters, int n_tokens, int n_req, int nq, int nkv, int d, int page_size, float scale,
-                                 int window, int max_q_len, int num_splits, int run_small, int run_tiles,
-                                 cudaStream_t stream) {
+template <bool TMA>
+static int att_launch(const CUtensorMap& map, int total_rows, int* err, const void* qkv, int row_stride, const void* pages,
+                      const int* block_tables, int bt_stride, const int* cu_q, const int* seq_lens, void* out, float* scratch,
+                      int* counters, int n_tokens, int n_req, int nq, int nkv, int page_size, float scale_log2, int window,
+                      int max_q_len, int num_splits, int run_small, int run_tiles, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_small_q_kernel<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_q_smem(TMA));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_tile_kernel<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem(TMA));
+    if (e != cudaSuccess) return -(int)e;
+    configured = true;
+  }
+  const int G = nq / nkv;
+  if (run_small) {
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n_tokens * nq * num_splits * D : nullptr;
+    dim3 grid(num_splits, nkv, n_req);
+    int st = ifb_launch(attn_small_q_kernel<TMA>, grid, dim3(THREADS), small_q_smem(TMA), stream, map, total_rows, err,
+                        (const bf16*)qkv, row_stride, (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out,
+                        part_o, part_ml, counters, nq, nkv, page_size, scale_log2, window, num_splits);
+    if (st) return st;
+  }
+  if (run_tiles) {
+    const int tpc = 4 * (16 / G);
+    dim3 grid((max_q_len + tpc - 1) / tpc, nkv, n_req);
+    return ifb_launch(attn_tile_kernel<TMA>, grid, dim3(THREADS), tile_smem(TMA), stream, map, total_rows, err, (const bf16*)qkv,
+                      row_stride, (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, nq, nkv, page_size,
+                      scale_log2, window);
+  }
+  return IFB_OK;
+}
+
+// max_q_len: the most query tokens any request brings.  run_small / run_tiles: which of the two kernels to
+// launch; requests are routed by rows = q_len * (nq / nkv) <= 16.  num_pages: pages of the pool `pages`.
+// err: a device int that stays 0 unless a bounded wait gave up (TMA path).  use_tma 0 forces the cp.async path.
+IFB_EXPORT int ifb_attention_mma(const void* qkv, int row_stride, const void* pages, long long num_pages,
+                                 const int* block_tables, int bt_stride, const int* cu_q, const int* seq_lens, void* out,
+                                 float* scratch, int* counters, int* err, int n_tokens, int n_req, int nq, int nkv, int d,
+                                 int page_size, float scale, int window, int max_q_len, int num_splits, int run_small,
+                                 int run_tiles, int use_tma, cudaStream_t stream) {
   if (n_tokens <= 0 || n_req <= 0) return IFB_OK;
   if (d != D) return IFB_ERR_SIZE;
   if (nkv < 1 || nq % nkv || page_size < 1 || window < 0 || num_splits < 1) return IFB_ERR_ARG;
@@ -459,30 +684,21 @@ IFB_EXPORT int ifb_attention_mma(const void* qkv, int row_stride, const void* pa
   if (G > 16 && run_tiles) return IFB_ERR_SIZE;
   if (row_stride % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)out & 3)) return IFB_ERR_ALIGN;
   if (n_req > 65535 || nkv > 65535) return IFB_ERR_SIZE;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_small_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_q_smem());
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem());
-    if (e != cudaSuccess) return -(int)e;
-    configured = true;
-  }
+  if (run_small && num_splits > 1 && (!scratch || !counters)) return IFB_ERR_ARG;
   const float scale_log2 = scale * 1.4426950408889634f;
-  if (run_small) {
-    if (num_splits > 1 && (!scratch || !counters)) return IFB_ERR_ARG;
-    float* part_o = scratch;
-    float* part_ml = scratch ? scratch + (size_t)n_tokens * nq * num_splits * D : nullptr;
-    dim3 grid(num_splits, nkv, n_req);
-    int st = ifb_launch(attn_small_q_kernel, grid, dim3(THREADS), small_q_smem(), stream, (const bf16*)qkv, row_stride,
-                        (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, part_o, part_ml, counters,
-                        nq, nkv, page_size, scale_log2, window, num_splits);
+  const long long rows = num_pages * 2 * nkv * page_size;
+  const bool tma = use_tma && TMA_D && err && (page_size == 16 || page_size == 32 || page_size == 64) && rows < 0x7fffffffLL &&
+                   ((uintptr_t)pages & 127) == 0;
+  CUtensorMap map;
+  if (tma) {
+    int st = kv_tensor_map(&map, pages, rows, page_size);
     if (st) return st;
+    return att_launch<true>(map, (int)rows, err, qkv, row_stride, pages, block_tables, bt_stride, cu_q, seq_lens, out, scratch,
+                            counters, n_tokens, n_req, nq, nkv, page_size, scale_log2, window, max_q_len, num_splits, run_small,
+                            run_tiles, stream);
   }
-  if (run_tiles) {
-    const int tpc = 4 * (16 / G);
-    dim3 grid((max_q_len + tpc - 1) / tpc, nkv, n_req);
-    return ifb_launch(attn_tile_kernel, grid, dim3(THREADS), tile_smem(), stream, (const bf16*)qkv, row_stride,
-                      (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, nq, nkv, page_size,
-                      scale_log2, window);
-  }
-  return IFB_OK;
+  memset(&map, 0, sizeof(map));
+  return att_launch<false>(map, 0, err, qkv, row_stride, pages, block_tables, bt_stride, cu_q, seq_lens, out, scratch, counters,
+                           n_tokens, n_req, nq, nkv, page_size, scale_log2, window, max_q_len, num_splits, run_small, run_tiles,
+                           stream);
 }

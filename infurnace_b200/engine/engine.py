@@ -59,6 +59,7 @@ class Engine:
         self.eos_token_ids = list(eos_token_ids)
         self._detoks: Dict[str, StreamingDetokenizer] = {}
         self._count = 0
+        self._steps_since_check = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -144,9 +145,9 @@ class Engine:
             ids = self.runner.step_and_sample(entries, temps, us)
             if sampled:
                 raw.tokens = {e.request_id: int(t) for e, t in zip(sampled, ids.tolist())}
-            check = getattr(self.runner.rt.kernels, "check_device_errors", None)
-            if check is not None:
-                check()
+            self._steps_since_check += 1
+            if self._steps_since_check >= 32:      # reading the kernels' error word costs a device round trip
+                self.check_device_errors()
         except Exception as e:  # a failed step fails its requests, not the engine
             if not isinstance(e, OutOfPages):
                 traceback.print_exc()
@@ -208,6 +209,14 @@ class Engine:
     def step(self) -> EngineStepResult:
         return self.commit_step(self.execute_step(self.prepare_step()))
 
+    def check_device_errors(self) -> None:
+        """Raise if a kernel recorded that a bounded wait on a barrier gave up since the last check
+        (done every 32 steps, and when ``generate`` ends)."""
+        self._steps_since_check = 0
+        check = getattr(self.runner.rt.kernels, "check_device_errors", None)
+        if check is not None:
+            check()
+
     # ------------------------------------------------------------------ conveniences
     def generate(self, prompts: Sequence[Sequence[int]], sampling_params=None) -> List[List[int]]:
         """Token ids in, generated token ids out, for a list of prompts (one
@@ -227,6 +236,7 @@ class Engine:
             idle_steps = 0 if moved else idle_steps + 1
             if idle_steps > 100:
                 raise RuntimeError("the scheduler made no progress in 100 steps")
+        self.check_device_errors()
         out = []
         for rid in ids:
             req = self.scheduler.get_request(rid)

@@ -80,8 +80,9 @@ class CudaKernels:
         self.gemv_max_rows = 64        # up to here: the kernel without global partial sums
         self.skinny_max_rows = 4096    # above this the plain kernel runs (until a large-tile kernel takes over)
         self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
-        self._tc_err = None            # device int: non-zero after a bounded wait in a tcgen05 kernel gave up
-        self._tc_used = False
+        self._dev_err = None           # device int: non-zero after a bounded barrier wait in a kernel gave up
+        self.attention_tma = True      # keys and values by TMA where the sizes allow (else 16-byte async copies)
+        self._err_armed = False
         self.tc_min_rows = 65
         self._attn_mma = {}        # head size -> library
         self._attn_scratch = None
@@ -158,21 +159,21 @@ class CudaKernels:
             self._tc = load_library("linear_tcgen05", progress=self._progress)
             self._tc.ifb_linear_tcgen05.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                     c_void_p, c_void_p]
-            self._tc_err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        if self._dev_err is None:
+            self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.launches += 1
-        self._tc_used = True
+        self._err_armed = True
         _check(self._tc.ifb_linear_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), n, o, k, epi,
-                                           self._tc_err.data_ptr(), self._stream()), "linear")
+                                           self._dev_err.data_ptr(), self._stream()), "linear")
 
     def check_device_errors(self):
         """Raise if a kernel recorded that one of its bounded waits gave up (synchronises)."""
-        if self._tc_used:
-            self._tc_used = False
-            code = int(self._tc_err.item())
+        if self._err_armed:
+            self._err_armed = False
+            code = int(self._dev_err.item())
             if code:
-                self._tc_err.zero_()
-                raise KernelError(f"a tcgen05 product gave up waiting on a barrier (code {code}: 1 producer, 2 issuer, "
-                                  "3 epilogue); its output is not valid")
+                self._dev_err.zero_()
+                raise KernelError(f"a kernel gave up waiting on a barrier (code {code}); its output is not valid")
 
     def _linear_gemv(self, x, w, out, n, o, k, epi):
         self.launches += 1
@@ -266,9 +267,9 @@ class CudaKernels:
         lib = self._attn_mma.get(head_dim)
         if lib is None:
             lib = load_library("attention_mma", {"HEAD_DIM": head_dim}, progress=self._progress)
-            lib.ifb_attention_mma.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                              c_int, c_int, c_int, c_int, c_void_p]
+            lib.ifb_attention_mma.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                              c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
             lib.ifb_attention_mma_scratch_floats.restype = c_longlong
             lib.ifb_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int]
             self._attn_mma[head_dim] = lib
@@ -306,11 +307,15 @@ class CudaKernels:
                 self.scratch_generation += 1
             counters = self._attn_counters
         self.launches += 1 + (0 if only_small else 1)
+        if self._dev_err is None:
+            self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self._err_armed = True
         _check(lib.ifb_attention_mma(
-            qkv.data_ptr(), qkv.stride(0), kv_pages.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
-            cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), _ptr(scratch), _ptr(counters), n, r, num_heads, num_kv_heads,
-            head_dim, kv_pages.shape[3], float(scale), int(window), int(max_q_len), int(num_splits), 1,
-            0 if only_small else 1, self._stream()), "paged_attention")
+            qkv.data_ptr(), qkv.stride(0), kv_pages.data_ptr(), kv_pages.shape[0], block_tables.data_ptr(),
+            block_tables.stride(0), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), _ptr(scratch), _ptr(counters),
+            self._dev_err.data_ptr(), n, r, num_heads, num_kv_heads, head_dim, kv_pages.shape[3], float(scale), int(window),
+            int(max_q_len), int(num_splits), 1, 0 if only_small else 1, 1 if self.attention_tma else 0, self._stream()),
+            "paged_attention")
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):
