@@ -113,6 +113,8 @@ class CacheManager:
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self._slot_of: Dict[str, int] = {}
         self._computed: Dict[str, int] = {}
+        self._epoch: Dict[str, int] = {}          # rid -> serial number of its current life (ids may be reused)
+        self._lives = 0
         if allocate_tensors:
             import torch
             for g in self.kv_groups:
@@ -146,6 +148,10 @@ class CacheManager:
     def slot_of(self, rid: str) -> int:
         return self._slot_of[rid]
 
+    def epoch_of(self, rid: str) -> int:
+        """A number that differs between two lives of the same request id."""
+        return self._epoch[rid]
+
     def block_table(self, rid: str, group: int) -> List[int]:
         return self.kv_groups[group].tables[rid]
 
@@ -173,6 +179,8 @@ class CacheManager:
         slot = self._free_slots.pop()
         self._slot_of[rid] = slot
         self._computed[rid] = 0
+        self._lives += 1
+        self._epoch[rid] = self._lives
         for g in self.kv_groups:
             g.tables[rid] = []
         for g in self.state_groups:
@@ -259,6 +267,7 @@ class CacheManager:
             g.pool.free([p for p in g.tables.pop(rid) if p != RELEASED])
         self._free_slots.append(self._slot_of.pop(rid))
         del self._computed[rid]
+        del self._epoch[rid]
 
     # ------------------------------------------------------------------ invariants
     def check(self) -> None:

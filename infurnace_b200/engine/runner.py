@@ -132,6 +132,9 @@ class ModelRunner:
              torch.full((max(g, 1), r, self.max_pages), RELEASED, dtype=torch.int32, pin_memory=self._pin))
             for _ in range(2)]
         self._stage_events = [None, None]
+        self._stage_np = [(a.numpy(), b.numpy()) for a, b in self._stage]      # the same memory, for cheap list writes
+        # block tables of live requests as arrays that grow with the tables: (epoch, synced length, array) by (rid, group)
+        self._table_rows: Dict[tuple, list] = {}
         self._dev_small = torch.zeros(self._small_len, dtype=torch.int32, device=dev)
         self._dev_tables = torch.full((max(g, 1), r, self.max_pages), RELEASED, dtype=torch.int32, device=dev)
         self.steps_run = 0
@@ -264,6 +267,25 @@ class ModelRunner:
         # the recording ran nothing; this step's result is the eager run's
         self._graphs[key] = (graph, stamp)
 
+    def _table_row(self, rid, gi):
+        """The block table of (request, group) as an int32 array, extended by the pages taken since last
+        time.  Entries of pages that a window released are left as they were: nothing reads them."""
+        import numpy as np
+        cache = self.cache
+        table = cache.block_table(rid, gi)
+        epoch = cache.epoch_of(rid)
+        held = self._table_rows.get((rid, gi))
+        if held is None or held[0] != epoch or held[1] > len(table):
+            if len(self._table_rows) > 8 * self.max_requests * max(1, len(cache.kv_groups)):
+                self._table_rows = {k: v for k, v in self._table_rows.items() if cache.has_request(k[0])}
+            held = [epoch, 0, np.empty(self.max_pages, dtype=np.int32)]
+            self._table_rows[(rid, gi)] = held
+        n = len(table)
+        if n > held[1]:
+            held[2][held[1]:n] = table[held[1]:n]
+            held[1] = n
+        return held[2][:n]
+
     # ------------------------------------------------------------------ metadata
     def _build_context(self, entries, temperatures=None, uniforms=None, pad_to=0, seq_bucket=0) -> StepContext:
         cache = self.cache
@@ -272,6 +294,7 @@ class ModelRunner:
         if self._stage_events[turn] is not None:
             self._stage_events[turn].synchronize()
         host_small, host_tables = self._stage[turn]
+        np_small, np_tables = self._stage_np[turn]
         ids, pos, req, rows, cu, seq, slots, first = [], [], [], [], [0], [], [], []
         group_slots = [[] for _ in cache.kv_groups]
         max_q = 0
@@ -290,9 +313,8 @@ class ModelRunner:
             max_q = max(max_q, n)
             for gi in range(len(cache.kv_groups)):
                 group_slots[gi].extend(cache.slots_for(e.request_id, gi, n))
-                table = cache.block_table(e.request_id, gi)
-                row = host_tables[gi, r]
-                row[: len(table)] = torch.tensor(table, dtype=torch.int32)
+                row = self._table_row(e.request_id, gi)
+                np_tables[gi, r, : len(row)] = row
         real_rows = len(rows)
         for j in range(len(entries), pad_to):      # padding of a graph bucket: tokens that store and see nothing
             ids.append(0); pos.append(0); req.append(j); rows.append(0)
@@ -307,26 +329,27 @@ class ModelRunner:
         o_slot = o_seq + r_max
         o_first = o_slot + r_max
         o_g = o_first + r_max
-        h[o_ids:o_ids + N] = torch.tensor(ids, dtype=torch.int32)
-        h[o_pos:o_pos + N] = torch.tensor(pos, dtype=torch.int32)
-        h[o_req:o_req + N] = torch.tensor(req, dtype=torch.int32)
+        h = np_small
+        h[o_ids:o_ids + N] = ids
+        h[o_pos:o_pos + N] = pos
+        h[o_req:o_req + N] = req
         if M:
-            h[o_rows:o_rows + M] = torch.tensor(rows, dtype=torch.int32)
-        h[o_cu:o_cu + R + 1] = torch.tensor(cu, dtype=torch.int32)
-        h[o_seq:o_seq + R] = torch.tensor(seq, dtype=torch.int32)
-        h[o_slot:o_slot + R] = torch.tensor(slots, dtype=torch.int32)
-        h[o_first:o_first + R] = torch.tensor(first, dtype=torch.int32)
+            h[o_rows:o_rows + M] = rows
+        h[o_cu:o_cu + R + 1] = cu
+        h[o_seq:o_seq + R] = seq
+        h[o_slot:o_slot + R] = slots
+        h[o_first:o_first + R] = first
         for gi, gs in enumerate(group_slots):
-            h[o_g + gi * n_max: o_g + gi * n_max + N] = torch.tensor(gs, dtype=torch.int32)
+            h[o_g + gi * n_max: o_g + gi * n_max + N] = gs
         o_f = o_g + len(group_slots) * n_max
         if temperatures is not None:
-            hf = h.view(torch.float32)
+            hf = h.view("float32")
             k = len(temperatures)
-            hf[o_f:o_f + r_max] = 0.0
-            hf[o_f + r_max:o_f + 2 * r_max] = 0.0
+            hf[o_f:o_f + 2 * r_max] = 0.0
             if k:
-                hf[o_f:o_f + k] = torch.tensor(list(map(float, temperatures)), dtype=torch.float32)
-                hf[o_f + r_max:o_f + r_max + k] = torch.tensor(list(map(float, uniforms)), dtype=torch.float32)
+                hf[o_f:o_f + k] = temperatures
+                hf[o_f + r_max:o_f + r_max + k] = uniforms
+        h = host_small
         d = self._dev_small
         d.copy_(h, non_blocking=True)
         if cache.kv_groups:
