@@ -482,7 +482,8 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, int
   const int q0 = cu_q[r], q_len = cu_q[r + 1] - q0, L = seq_lens[r];
   if (q_len * G <= 16) return;                               // the small-q kernel's request
   const int tpw = 16 / G, tpc = 4 * tpw;                     // tokens per warp, per CTA
-  const int t0 = blockIdx.x * tpc;
+  // the last query tiles have the longest key ranges: they go first, so that the grid's tail is short work
+  const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * tpc;
   if (t0 >= q_len) return;
   const int t1 = min(q_len, t0 + tpc);
   const int p_first = L - q_len;

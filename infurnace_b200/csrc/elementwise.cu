@@ -140,6 +140,93 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int n_tokens, int
   }
 }
 
+// The same for the common shape: the whole head is rotated in the half-split pairing (or nothing is) and the head
+// size is 32 * EPL with EPL in {2, 4, 8}.  A lane keeps EPL consecutive elements in registers (one vector load and
+// store), the element's partner in the rotation sits in lane ^ 16, and no shared memory is used.
+template <typename T, int EPL> struct alignas(sizeof(T) * EPL) QkVec { T v[EPL]; };
+
+constexpr int QK_HPW = 4;      // heads of one token that a warp of the vector kernel handles: the angles are computed once for them
+
+template <typename T, int EPL>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv, const void* __restrict__ qw,
+                              const void* __restrict__ kw, int w_dtype, float eps, const float* __restrict__ inv_freq,
+                              const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ pages,
+                              int page_size) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  constexpr int d = 32 * EPL;
+  typedef QkVec<T, EPL> Vec;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const int blocks_per_token = (heads + QK_HPW - 1) / QK_HPW;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (item >= (long long)n_tokens * blocks_per_token) return;
+  const int tok = (int)(item / blocks_per_token), head0 = (int)(item % blocks_per_token) * QK_HPW;
+  const int slot = slots ? slots[tok] : -1;
+  // cos and sin of this lane's EPL angles, once for all heads of the block (lanes l and l ^ 16 share them)
+  float cs[EPL], sn[EPL];
+  if (inv_freq != nullptr && head0 < nq + nkv) {
+    const float pos = (float)positions[tok];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) sincosf(pos * inv_freq[(lane & 15) * EPL + e], &sn[e], &cs[e]);
+  }
+  for (int head = head0; head < min(heads, head0 + QK_HPW); ++head) {
+    T* src = qkv + (size_t)tok * heads * d + (size_t)head * d + lane * EPL;
+    const bool is_v = head >= nq + nkv, is_k = head >= nq && !is_v;
+    T* dst = nullptr;
+    if (slot >= 0 && head >= nq) {
+      const int kvh = is_v ? head - nq - nkv : head - nq;
+      dst = pages + ((((size_t)(slot / page_size) * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + (slot % page_size)) * d + lane * EPL;
+    }
+    if (is_v) {
+      if (dst) *reinterpret_cast<Vec*>(dst) = *reinterpret_cast<const Vec*>(src);
+      continue;
+    }
+    const void* w = is_k ? kw : qw;
+    const bool rotate = inv_freq != nullptr;
+    if (!w && !rotate && !dst) continue;
+    const Vec in = *reinterpret_cast<const Vec*>(src);
+    float v[EPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) { v[e] = to_f32<T>(in.v[e]); ss += v[e] * v[e]; }
+    if (w) {
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) v[e] = v[e] * r * load_as_f32(w, w_dtype, lane * EPL + e);
+    }
+    if (rotate) {
+      const bool first = lane < 16;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const float o = __shfl_xor_sync(0xffffffffu, v[e], 16);
+        v[e] = first ? v[e] * cs[e] - o * sn[e] : v[e] * cs[e] + o * sn[e];
+      }
+    }
+    Vec res;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) res.v[e] = from_f32<T>(v[e]);
+    if (w || rotate) *reinterpret_cast<Vec*>(src) = res;
+    if (dst) *reinterpret_cast<Vec*>(dst) = res;
+  }
+}
+
+template <typename T>
+static int qk_vec_launch(int epl, unsigned blocks, cudaStream_t stream, T* qkv, int n_tokens, int nq, int nkv, const void* qw,
+                         const void* kw, int w_dtype, float eps, const float* inv_freq, const int* positions, const int* slots,
+                         T* pages, int page_size) {
+  if (epl == 2)
+    return ifb_launch(qk_norm_rope_store_vec_kernel<T, 2>, dim3(blocks), dim3(128), 0, stream, qkv, n_tokens, nq, nkv, qw, kw,
+                      w_dtype, eps, inv_freq, positions, slots, pages, page_size);
+  if (epl == 4)
+    return ifb_launch(qk_norm_rope_store_vec_kernel<T, 4>, dim3(blocks), dim3(128), 0, stream, qkv, n_tokens, nq, nkv, qw, kw,
+                      w_dtype, eps, inv_freq, positions, slots, pages, page_size);
+  return ifb_launch(qk_norm_rope_store_vec_kernel<T, 8>, dim3(blocks), dim3(128), 0, stream, qkv, n_tokens, nq, nkv, qw, kw,
+                    w_dtype, eps, inv_freq, positions, slots, pages, page_size);
+}
+
 IFB_EXPORT int ifb_qk_norm_rope_store(void* qkv, int dtype, int n_tokens, int nq, int nkv, int d, const void* qw,
                                       const void* kw, int w_dtype, float eps, const float* inv_freq, int rotary_dim,
                                       int interleaved, const int* positions, const int* slots, void* pages,
@@ -152,6 +239,16 @@ IFB_EXPORT int ifb_qk_norm_rope_store(void* qkv, int dtype, int n_tokens, int nq
   const int warps = 4;
   const long long items = (long long)n_tokens * (nq + 2 * nkv);
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+  if ((d == 64 || d == 128 || d == 256) && (!inv_freq || (rotary_dim == d && !interleaved)) &&
+      (dtype == IFB_F32 || dtype == IFB_BF16) && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)pages & 15) == 0) {
+    const long long vitems = (long long)n_tokens * ((nq + 2 * nkv + QK_HPW - 1) / QK_HPW);
+    const unsigned vblocks = (unsigned)((vitems + warps - 1) / warps);
+    if (dtype == IFB_F32)
+      return qk_vec_launch<float>(d / 32, vblocks, stream, (float*)qkv, n_tokens, nq, nkv, qw, kw, w_dtype, eps, inv_freq,
+                                  positions, slots, (float*)pages, page_size);
+    return qk_vec_launch<__nv_bfloat16>(d / 32, vblocks, stream, (__nv_bfloat16*)qkv, n_tokens, nq, nkv, qw, kw, w_dtype, eps,
+                                        inv_freq, positions, slots, (__nv_bfloat16*)pages, page_size);
+  }
   const size_t smem = (size_t)warps * d * sizeof(float);
   if (dtype == IFB_F32)
     return ifb_launch(qk_norm_rope_store_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream, (float*)qkv, n_tokens,

@@ -84,7 +84,9 @@ def test_linear(K, xd, wd, od, n, o, k, epilogue):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,rdim,inter,ps", [(4, 2, 16, 16, False, 16), (6, 3, 48, 48, False, 8),
-                                                    (5, 1, 80, 32, True, 5), (8, 8, 128, 128, False, 16)])
+                                                    (5, 1, 80, 32, True, 5), (8, 8, 128, 128, False, 16),
+                                                    (4, 2, 64, 64, False, 16), (2, 1, 256, 256, False, 32),
+                                                    (2, 2, 128, 64, False, 16), (2, 2, 64, 64, True, 16)])
 def test_qk_norm_rope_store(K, dtype, nq, nkv, d, rdim, inter, ps):
     n, pages = 23, 9
     qkv = rnd((n, (nq + 2 * nkv) * d), dtype, 6)
