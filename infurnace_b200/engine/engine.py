@@ -24,7 +24,7 @@ from ..tokenizer import StreamingDetokenizer, Tokenizer, check_stop_strings
 from .loading import EngineOptions, build_runner
 from .request import Request, RequestMetrics, RequestState, SamplingParams
 from .runner import StepEntry
-from .scheduler import Scheduler, StepPlan
+from .scheduler import PlannedEntry, Scheduler, StepPlan
 
 
 @dataclass(frozen=True)
@@ -43,7 +43,10 @@ class EngineStepResult:
 
 @dataclass
 class RawStep:
+    """A step that was launched: its plan, and the sampled token ids on their way to the host."""
     plan: StepPlan
+    handle: object = None                  # SampledTokens of the step (None: nothing was sampled)
+    sampled: List[str] = field(default_factory=list)     # request ids, in the order of the handle's rows
     tokens: Dict[str, int] = field(default_factory=dict)
     error: Optional[str] = None
 
@@ -60,6 +63,8 @@ class Engine:
         self._detoks: Dict[str, StreamingDetokenizer] = {}
         self._count = 0
         self._steps_since_check = 0
+        self._inflight: Optional[RawStep] = None       # a step launched ahead of the one being committed
+        self.overlap_decode = True
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -125,13 +130,16 @@ class Engine:
         return d.text if d else ""
 
     def is_done(self) -> bool:
-        return self.scheduler.is_idle
+        return self.scheduler.is_idle and self._inflight is None
 
     # ------------------------------------------------------------------ the three phases of a step
     def prepare_step(self) -> StepPlan:
         return self.scheduler.schedule()
 
-    def execute_step(self, plan: StepPlan) -> RawStep:
+    def execute_step(self, plan: StepPlan, feed=None, pending: int = 0) -> RawStep:
+        """Launch the plan's step; nothing here waits for the device.  ``feed`` and ``pending`` are for a
+        step that is launched while the one before it is still in flight (see ``step``): its input
+        tokens come from the device, and each request's draw counter is ``pending`` ahead."""
         raw = RawStep(plan)
         if not plan.entries:
             return raw
@@ -140,14 +148,13 @@ class Engine:
             sampled = [e for e in plan.entries if e.sample]
             reqs = [self.scheduler.get_request(e.request_id) for e in sampled]
             temps = [r.sampling_params.effective_temperature for r in reqs]
-            us = [uniform(r.sampling_params.seed, len(r.output_token_ids)) if t > 0.0 else 0.0
+            us = [uniform(r.sampling_params.seed, len(r.output_token_ids) + pending) if t > 0.0 else 0.0
                   for r, t in zip(reqs, temps)]
-            ids = self.runner.step_and_sample(entries, temps, us)
-            if sampled:
-                raw.tokens = {e.request_id: int(t) for e, t in zip(sampled, ids.tolist())}
+            raw.handle = self.runner.step_and_sample(entries, temps, us, feed=feed)
+            raw.sampled = [e.request_id for e in sampled]
+            for e in plan.entries:                 # the tokens' keys and values are in the pages now
+                self.scheduler.advance(e)
             self._steps_since_check += 1
-            if self._steps_since_check >= 32:      # reading the kernels' error word costs a device round trip
-                self.check_device_errors()
         except Exception as e:  # a failed step fails its requests, not the engine
             if not isinstance(e, OutOfPages):
                 traceback.print_exc()
@@ -156,6 +163,10 @@ class Engine:
 
     def commit_step(self, raw: RawStep) -> EngineStepResult:
         plan, sch = raw.plan, self.scheduler
+        if raw.error is None and raw.handle is not None:
+            raw.tokens = {rid: int(t) for rid, t in zip(raw.sampled, raw.handle.tolist())}
+            if self._steps_since_check >= 32:      # reading the kernels' error word costs a device round trip
+                self.check_device_errors()
         completed, failed = [], list(plan.failed)
         new_tokens: Dict[str, List[int]] = {}
         new_text: Dict[str, str] = {}
@@ -173,7 +184,6 @@ class Engine:
                 n_decode += len(e.tokens)
             else:
                 n_prefill += len(e.tokens)
-            sch.advance(e)
             if not e.sample:
                 continue
             tok = raw.tokens[e.request_id]
@@ -207,7 +217,48 @@ class Engine:
             free_pages=tuple(self.runner.cache.free_pages()))
 
     def step(self) -> EngineStepResult:
-        return self.commit_step(self.execute_step(self.prepare_step()))
+        """One step's results.  While requests only decode, the next step is launched before this
+        one's tokens are read (``overlap_decode``): its input tokens are taken on the device from
+        what this step sampled, so the host's share of a step (planning, staging, reading back)
+        runs beside the device's.  A request that turns out to have stopped on this step's token
+        has then computed one token too many, which is dropped with the request."""
+        if self._inflight is None:
+            self._inflight = self.execute_step(self.prepare_step())
+        current, self._inflight = self._inflight, None
+        if self.overlap_decode and current.error is None:
+            ahead = self._plan_ahead(current)
+            if ahead is not None:
+                plan, rows = ahead
+                self._inflight = self.execute_step(plan, feed=(current.handle, rows), pending=1)
+        return self.commit_step(current)
+
+    def _plan_ahead(self, current: RawStep):
+        """The step after ``current`` if it is plain: every entry of ``current`` decoded one token, nobody
+        waits, and each of those requests, unless this token is its last by count, decodes one more."""
+        sch, cache = self.scheduler, self.runner.cache
+        plan = current.plan
+        if not plan.entries or plan.preempted or plan.failed or sch.num_waiting or current.handle is None:
+            return None
+        if len(plan.entries) != sch.num_running:
+            return None
+        entries, rows, reserved = [], [], [0] * len(cache.free_pages())
+        for i, e in enumerate(plan.entries):
+            req = sch.get_request(e.request_id)
+            if len(e.tokens) != 1 or not e.sample or req.state is not RequestState.DECODING:
+                return None
+            sp = req.sampling_params
+            produced = len(req.output_token_ids) + 1          # with the token that is on its way
+            if produced >= sp.min_tokens and produced >= sp.max_tokens:
+                continue                                       # it ends with that token, whatever it is
+            if req.num_tokens + 1 >= self.runner.max_model_len or not cache.can_allocate(e.request_id, 1, reserved):
+                return None
+            for g, p in enumerate(cache.pages_needed(e.request_id, 1)):
+                reserved[g] += p
+            entries.append(PlannedEntry(e.request_id, req.num_computed_tokens, (-1,), True))
+            rows.append(i)
+        if not entries:
+            return None
+        return StepPlan(entries=entries), rows
 
     def check_device_errors(self) -> None:
         """Raise if a kernel recorded that a bounded wait on a barrier gave up since the last check
@@ -269,6 +320,8 @@ def generate(engine: Engine, prompt: Sequence[int], max_tokens: int):
             else:
                 decode_times.append(dt)
             t0 = time.perf_counter()
+    while not engine.is_done():            # a step launched ahead for the finished request
+        engine.step()
     if req.state is not RequestState.FINISHED:
         raise RuntimeError(f"generation ended {req.state.value}: {req.error}")
     if decode_times:

@@ -43,6 +43,19 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+class SampledTokens:
+    """The token ids one step sampled, on their way to the host: a device copy that the next step may
+    take its input tokens from, and a pinned host copy that ``tolist`` waits for."""
+
+    def __init__(self, device, host, event, count, slot):
+        self.device, self.host, self.event, self.count, self.slot = device, host, event, count, slot
+
+    def tolist(self):
+        if self.event is not None:
+            self.event.synchronize()
+        return self.host[: self.count].tolist()
+
+
 @dataclass
 class KVView:
     """What a mixer gets for its cache entry: the entry's pages and its group's tables."""
@@ -139,6 +152,10 @@ class ModelRunner:
         self._dev_tables = torch.full((max(g, 1), r, self.max_pages), RELEASED, dtype=torch.int32, device=dev)
         self.steps_run = 0
         self.sampled = torch.zeros(max(r, 1), dtype=torch.int32, device=dev)
+        # the sampled ids of the last two steps (a step in flight may feed the next one from the device)
+        self._hist = [torch.zeros(max(r, 1), dtype=torch.int32, device=dev) for _ in range(2)]
+        self._hist_host = [torch.zeros(max(r, 1), dtype=torch.int32, pin_memory=self._pin) for _ in range(2)]
+        self._sampled_steps = 0
         # decode-only steps are replayed from CUDA graphs, one per (batch bucket, context bucket)
         self.use_graphs = self._pin and bool(getattr(model, "graph_safe", False))
         self._graphs: Dict[tuple, tuple] = {}
@@ -146,7 +163,7 @@ class ModelRunner:
         self.launches_per_graph_step = 0
 
     # ------------------------------------------------------------------ the step
-    def validate(self, entries: Sequence[StepEntry]) -> None:
+    def validate(self, entries: Sequence[StepEntry], placeholders: bool = False) -> None:
         if not entries:
             raise BatchError("a step needs at least one entry")
         if len(entries) > self.max_requests:
@@ -164,7 +181,7 @@ class ModelRunner:
             if n < 1:
                 raise BatchError(f"request {e.request_id!r} brings no tokens")
             for t in e.tokens:
-                if not 0 <= int(t) < vocab:
+                if not placeholders and not 0 <= int(t) < vocab:
                     raise BatchError(f"token id {t} of request {e.request_id!r} is outside the vocabulary of {vocab}")
             for w in e.want:
                 if not 0 <= int(w) < n:
@@ -203,12 +220,19 @@ class ModelRunner:
         return logits
 
     def step_and_sample(self, entries: Sequence[StepEntry], temperatures: Sequence[float],
-                        uniforms: Sequence[float]) -> Optional[torch.Tensor]:
-        """``step`` followed by the sampling kernel on the wanted rows: returns the int32 token
-        ids on the device (None if nothing is wanted).  ``temperatures`` and ``uniforms`` have
-        one entry per wanted row.  A step in which every request brings one token and wants its
-        logits (plain decoding) is replayed from a CUDA graph."""
-        self.validate(entries)
+                        uniforms: Sequence[float], feed=None) -> Optional[SampledTokens]:
+        """``step`` followed by the sampling kernel on the wanted rows: returns the sampled token
+        ids as a :class:`SampledTokens` (None if nothing is wanted); nothing here waits for the
+        device.  ``temperatures`` and ``uniforms`` have one entry per wanted row.  A step in which
+        every request brings one token and wants its logits (plain decoding) is replayed from a
+        CUDA graph.
+
+        ``feed`` = (previous step's SampledTokens, rows): the step's input tokens are not known
+        to the host yet; entry i takes row ``rows[i]`` of what the previous step sampled, on the
+        device (every entry then brings exactly one token, whose id in ``tokens`` is ignored)."""
+        if feed is not None and (len(feed[1]) != len(entries) or any(len(e.tokens) != 1 for e in entries)):
+            raise BatchError("a step fed from the device brings one token per entry and one source row per entry")
+        self.validate(entries, placeholders=feed is not None)
         wanted = sum(len(e.want) for e in entries)
         if len(temperatures) != wanted or len(uniforms) != wanted:
             raise BatchError("one temperature and one uniform number per wanted row")
@@ -216,14 +240,38 @@ class ModelRunner:
         decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         greedy = all(t == 0.0 for t in temperatures)
         if self.use_graphs and decode_only:
-            self._graph_step(entries, temperatures, uniforms, greedy)
+            self._graph_step(entries, temperatures, uniforms, greedy, feed)
         else:
             ctx = self._build_context(entries, temperatures=temperatures, uniforms=uniforms)
+            self._apply_feed(ctx, feed)
             self._forward_and_sample(ctx, greedy)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
-        return self.sampled[:wanted] if wanted else None
+        if not wanted:
+            return None
+        slot = self._sampled_steps % 2
+        self._sampled_steps += 1
+        dev, host = self._hist[slot], self._hist_host[slot]
+        dev[:wanted].copy_(self.sampled[:wanted])
+        host[:wanted].copy_(dev[:wanted], non_blocking=True)
+        event = None
+        if self._pin:
+            event = torch.cuda.Event()
+            event.record()
+        return SampledTokens(dev, host, event, wanted, slot)
+
+    def _apply_feed(self, ctx, feed) -> None:
+        """Overwrite the step's token ids on the device with rows of the previous step's sampled ids."""
+        if feed is None:
+            return
+        prev, rows = feed
+        n = len(rows)
+        if list(rows) == list(range(n)):
+            ctx.token_ids[:n].copy_(prev.device[:n])
+        else:
+            idx = torch.tensor(list(rows), dtype=torch.int64, device=prev.device.device)
+            ctx.token_ids[:n].copy_(prev.device.index_select(0, idx))
 
     def _forward_and_sample(self, ctx, greedy: bool):
         logits = self.model.forward(ctx)
@@ -235,7 +283,7 @@ class ModelRunner:
                 self.rt.kernels.sample(logits, ctx.temperatures[:m], ctx.uniforms[:m], self.sampled[:m])
         return logits
 
-    def _graph_step(self, entries, temperatures, uniforms, greedy) -> None:
+    def _graph_step(self, entries, temperatures, uniforms, greedy, feed=None) -> None:
         r = len(entries)
         r_bucket = 1
         while r_bucket < r:
@@ -248,6 +296,7 @@ class ModelRunner:
         key = (r_bucket, seq_bucket, greedy)
         ctx = self._build_context(entries, temperatures=temperatures, uniforms=uniforms, pad_to=r_bucket,
                                   seq_bucket=seq_bucket)
+        self._apply_feed(ctx, feed)
         stamp = (self.arena.generation, getattr(self.rt.kernels, "scratch_generation", 0))
         held = self._graphs.get(key)
         if held is not None and held[1] == stamp:
@@ -302,7 +351,7 @@ class ModelRunner:
             start = cache.num_computed(e.request_id)
             n = len(e.tokens)
             base = len(ids)
-            ids.extend(int(t) for t in e.tokens)
+            ids.extend(max(0, int(t)) for t in e.tokens)
             pos.extend(range(start, start + n))
             req.extend([r] * n)
             rows.extend(base + int(w) for w in e.want)

@@ -100,7 +100,7 @@ def test_a_failing_step_fails_its_requests_and_the_engine_goes_on(models, monkey
     eng.add_request(Request("a", [1, 2, 3], SamplingParams(max_tokens=4)))
     real = eng.runner.step_and_sample
     monkeypatch.setattr(eng.runner, "step_and_sample",
-                        lambda *a: (_ for _ in ()).throw(RuntimeError("device fell over")))
+                        lambda *a, **kw: (_ for _ in ()).throw(RuntimeError("device fell over")))
     res = eng.step()
     assert res.failed_requests == ("a",)
     a = eng.scheduler.get_request("a")
@@ -108,6 +108,30 @@ def test_a_failing_step_fails_its_requests_and_the_engine_goes_on(models, monkey
     assert eng.runner.cache.free_pages() == [40] and eng.is_done()
     monkeypatch.setattr(eng.runner, "step_and_sample", real)
     assert len(eng.generate([[4, 5, 6]], SamplingParams(max_tokens=3))[0]) == 3
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_launching_ahead_changes_no_token(models, temperature):
+    """Decode steps launched before the previous step's tokens are read (input tokens taken on the
+    device) give the tokens of the plain one-step-at-a-time loop: with stop tokens that cut requests
+    short (the token computed too many is dropped), different lengths, and more requests than slots."""
+    cfg, w = P.read_model(models["B"])
+    prompts = [tiny.random_tokens(320, n, 40 + n) for n in (5, 19, 33, 8, 50, 3)]
+    base = engine(models["B"], "B", max_num_seqs=3)
+    base.overlap_decode = False
+    free_run = base.generate(prompts, SamplingParams(max_tokens=20, temperature=temperature, seed=5))
+    stops = sorted({t[7] for t in free_run} | {free_run[0][2]})       # tokens that really occur: requests stop early
+    sps = [SamplingParams(max_tokens=10 + 3 * i, temperature=temperature, seed=5, stop_token_ids=stops, min_tokens=i % 3)
+           for i in range(len(prompts))]
+    outs = {}
+    for overlap in (False, True):
+        eng = engine(models["B"], "B", max_num_seqs=3)
+        eng.overlap_decode = overlap
+        outs[overlap] = eng.generate(prompts, sps)
+        eng.runner.cache.check()
+        assert eng.runner.cache.free_pages() == [40, 40] and eng.is_done()
+    assert outs[True] == outs[False]
+    assert any(len(o) < sp.max_tokens for o, sp in zip(outs[True], sps))       # some did stop on a stop token
 
 
 def test_cancel_between_steps(models):

@@ -125,3 +125,25 @@ def test_tool_style_entry_point_and_command_line(models, tmp_path):
                          capture_output=True, text=True, timeout=300, cwd=root)
     assert out.returncode == 0, out.stderr
     assert len(out.stdout.rstrip("\n")) == 5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_launching_ahead_changes_no_token_on_the_gpu(models, dtype):
+    """Graph-replayed decode steps launched before the previous step's tokens are read, against the
+    one-step-at-a-time loop: stop tokens cut requests short, lengths differ, requests outnumber slots."""
+    prompts = [tiny.random_tokens(320, n, 40 + n) for n in (5, 19, 33, 8, 50, 3)]
+    base = engine(models["B"], "B", dtype, max_num_seqs=3)
+    base.overlap_decode = False
+    free_run = base.generate(prompts, SamplingParams(max_tokens=20, temperature=0.9, seed=5))
+    stops = sorted({t[7] for t in free_run} | {free_run[0][2]})
+    sps = [SamplingParams(max_tokens=10 + 3 * i, temperature=0.9, seed=5, stop_token_ids=stops, min_tokens=i % 3)
+           for i in range(len(prompts))]
+    outs = {}
+    for overlap in (False, True):
+        eng = engine(models["B"], "B", dtype, max_num_seqs=3)
+        eng.overlap_decode = overlap
+        outs[overlap] = eng.generate(prompts, sps)
+        eng.runner.cache.check()
+        assert eng.is_done() and eng.runner.graph_replays > 0
+    assert outs[True] == outs[False]
+    assert any(len(o) < sp.max_tokens for o, sp in zip(outs[True], sps))
