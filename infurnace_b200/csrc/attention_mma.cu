@@ -262,6 +262,89 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[KB][4], const bf16* 
 
 constexpr int NO_ROW = -1000000000;
 
+// The end of a small-q CTA: its four consumer warps' (m, l, o) are merged through shared memory (`scratch`, at least
+// 4*16*D + 128 floats, free by now); then the output row is written, or with several splits the partial sums go to
+// global memory and the CTA that arrives last for its (request, key/value head) merges the splits in split order.
+// Every thread of the CTA calls this (threads of warps above 3 only keep the barriers company).
+__device__ __forceinline__ void small_q_finish(float* scratch, float (&m)[2], float (&l)[2], float (&o)[D / 8][4], int rows,
+                                               int G, int q0, int kvh, int r, int split, int num_splits, int nq, int nkv,
+                                               bf16* __restrict__ out, float* __restrict__ part_o,
+                                               float* __restrict__ part_ml, int* __restrict__ counters, int* is_last_p) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nthreads = blockDim.x;
+  const int rowA = lane >> 2, rowB = rowA + 8;
+  float* sm_o = scratch;                                     // [4][16][D]
+  float* sm_m = sm_o + 4 * 16 * D;                           // [4][16]
+  float* sm_l = sm_m + 64;                                   // [4][16]
+  if (warp < 4) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      l[e] += __shfl_xor_sync(0xffffffffu, l[e], 1);
+      l[e] += __shfl_xor_sync(0xffffffffu, l[e], 2);
+    }
+    if ((lane & 3) == 0) {
+      sm_m[warp * 16 + rowA] = m[0]; sm_m[warp * 16 + rowB] = m[1];
+      sm_l[warp * 16 + rowA] = l[0]; sm_l[warp * 16 + rowB] = l[1];
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int col = n * 8 + ((lane & 3) << 1);
+      float* pa = sm_o + ((size_t)warp * 16 + rowA) * D + col;
+      float* pb = sm_o + ((size_t)warp * 16 + rowB) * D + col;
+      pa[0] = o[n][0]; pa[1] = o[n][1]; pb[0] = o[n][2]; pb[1] = o[n][3];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows * D; idx += nthreads) {
+    const int row = idx / D, dim = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
+    const float U = M == -INFINITY ? 0.f : M;
+    float den = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(sm_m[w * 16 + row] - U);
+      den += sm_l[w * 16 + row] * f;
+      acc += sm_o[((size_t)w * 16 + row) * D + dim] * f;
+    }
+    const int tok = q0 + row / G, head = kvh * G + row % G;
+    if (num_splits == 1) {
+      out[((size_t)tok * nq + head) * D + dim] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+    } else {
+      const size_t base = ((size_t)tok * nq + head) * num_splits + split;
+      part_o[base * D + dim] = acc;
+      if (dim == 0) { part_ml[base * 2] = M; part_ml[base * 2 + 1] = den; }
+    }
+  }
+  if (num_splits == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&counters[r * nkv + kvh], 1);
+    *is_last_p = (old == num_splits - 1);
+  }
+  __syncthreads();
+  if (!*is_last_p) return;
+  __threadfence();
+  for (int idx = tid; idx < rows * D; idx += nthreads) {
+    const int row = idx / D, dim = idx % D;
+    const int tok = q0 + row / G, head = kvh * G + row % G;
+    const size_t base = ((size_t)tok * nq + head) * num_splits;
+    float M = -INFINITY;
+    for (int sp = 0; sp < num_splits; ++sp) M = fmaxf(M, part_ml[(base + sp) * 2]);
+    const float U = M == -INFINITY ? 0.f : M;
+    float den = 0.f, acc = 0.f;
+    for (int sp = 0; sp < num_splits; ++sp) {
+      const float f = exp2f(part_ml[(base + sp) * 2] - U);
+      den += part_ml[(base + sp) * 2 + 1] * f;
+      acc += part_o[(base + sp) * D + dim] * f;
+    }
+    out[((size_t)tok * nq + head) * D + dim] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+  }
+  if (tid == 0) counters[r * nkv + kvh] = 0;       // ready for the next launch
+}
+
 // --------------------------------------------------------------------------------------------
 // small-q kernel: grid (num_splits, kv heads, requests)
 // --------------------------------------------------------------------------------------------
@@ -384,76 +467,115 @@ attn_small_q_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, 
     return;
   }
   __syncthreads();
-  // merge the four warps' (m, l, o) through shared memory (the tile buffers are free now)
-  float* sm_o = reinterpret_cast<float*>(KV);                // [4][16][D]
-  float* sm_m = sm_o + 4 * 16 * D;                           // [4][16]
-  float* sm_l = sm_m + 64;                                   // [4][16]
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    l[e] += __shfl_xor_sync(0xffffffffu, l[e], 1);
-    l[e] += __shfl_xor_sync(0xffffffffu, l[e], 2);
-  }
-  if ((lane & 3) == 0) {
-    sm_m[warp * 16 + rowA] = m[0]; sm_m[warp * 16 + rowB] = m[1];
-    sm_l[warp * 16 + rowA] = l[0]; sm_l[warp * 16 + rowB] = l[1];
-  }
-#pragma unroll
-  for (int n = 0; n < D / 8; ++n) {
-    const int col = n * 8 + ((lane & 3) << 1);
-    float* pa = sm_o + ((size_t)warp * 16 + rowA) * D + col;
-    float* pb = sm_o + ((size_t)warp * 16 + rowB) * D + col;
-    pa[0] = o[n][0]; pa[1] = o[n][1]; pb[0] = o[n][2]; pb[1] = o[n][3];
-  }
-  __syncthreads();
-  for (int idx = tid; idx < rows * D; idx += THREADS) {
-    const int row = idx / D, dim = idx % D;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
-    const float U = M == -INFINITY ? 0.f : M;
-    float den = 0.f, acc = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float f = exp2f(sm_m[w * 16 + row] - U);
-      den += sm_l[w * 16 + row] * f;
-      acc += sm_o[((size_t)w * 16 + row) * D + dim] * f;
-    }
-    const int tok = q0 + row / G, head = kvh * G + row % G;
-    if (num_splits == 1) {
-      out[((size_t)tok * nq + head) * D + dim] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
-    } else {
-      const size_t base = ((size_t)tok * nq + head) * num_splits + split;
-      part_o[base * D + dim] = acc;
-      if (dim == 0) { part_ml[base * 2] = M; part_ml[base * 2 + 1] = den; }
-    }
-  }
-  if (num_splits == 1) return;
-  // the CTA that finishes last for this (request, key/value head) merges the splits, in split order
-  __threadfence();
-  __syncthreads();
+  small_q_finish(reinterpret_cast<float*>(KV), m, l, o, rows, G, q0, kvh, r, split, num_splits, nq, nkv, out, part_o, part_ml,
+                 counters, &is_last);
+}
+
+// --------------------------------------------------------------------------------------------
+// small-q kernel, TMA form with a producer warp: grid (num_splits, kv heads, requests), 160 threads.
+// Warps 0-3 are the consumers (16 keys of every tile each, as above); warp 4 only issues TMA loads.  A stage has a
+// "full" barrier (armed with the tile's bytes by the producer) and an "empty" barrier (one arrival per consumer warp
+// when it has read the tile), so no warp waits for another at a tile's end: a slow warp holds back only the refill
+// of its own stage.
+// --------------------------------------------------------------------------------------------
+constexpr int WS_THREADS = 160;
+__device__ __forceinline__ void att_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(WS_THREADS)
+attn_small_q_ws_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, int* __restrict__ err,
+                       const bf16* __restrict__ qkv, int row_stride, const int* __restrict__ block_tables, int bt_stride,
+                       const int* __restrict__ cu_q, const int* __restrict__ seq_lens, bf16* __restrict__ out,
+                       float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nq,
+                       int nkv, int page_size, float scale_log2, int window, int num_splits) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int is_last;
+  __shared__ uint64_t full_bar[SQ_STAGES], empty_bar[SQ_STAGES];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  constexpr int STAGE = 2 * BN * D;
+  const uint32_t raw = smem_u32(smem_raw);
+  bf16* KV = reinterpret_cast<bf16*>(smem_raw + (((raw + 1023u) & ~1023u) - raw));
+  bf16* Qs = KV + SQ_STAGES * STAGE;                          // [16][DP]
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = nq / nkv;
+  const int q0 = cu_q[r], q_len = cu_q[r + 1] - q0, L = seq_lens[r];
+  const int rows = q_len * G;
+  if (q_len <= 0 || rows > 16) return;
+  const int p_first = L - q_len;
+  const int lo = window > 0 ? max(0, p_first - window + 1) : 0, hi = L - 1;
+  const int total = hi + 1 - lo;
+  int per = total > 0 ? (total + num_splits - 1) / num_splits : 0;
+  per = (per + BN - 1) / BN * BN;
+  const int k_begin = lo + split * per, k_end = min(hi + 1, k_begin + per);
+  const int T0 = (k_begin / BN) * BN;
+  const int n_tiles = k_end > k_begin ? (k_end - T0 + BN - 1) / BN : 0;
+  const int* bt = block_tables + (size_t)r * bt_stride;
+  const int ps_shift = __ffs(page_size) - 1;
   if (tid == 0) {
-    const int old = atomicAdd(&counters[r * nkv + kvh], 1);
-    is_last = (old == num_splits - 1);
+    for (int st = 0; st < SQ_STAGES; ++st) { att_mbar_init(&full_bar[st], 1); att_mbar_init(&empty_bar[st], 4); }
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  for (int idx = tid; idx < rows * D; idx += THREADS) {
-    const int row = idx / D, dim = idx % D;
-    const int tok = q0 + row / G, head = kvh * G + row % G;
-    const size_t base = ((size_t)tok * nq + head) * num_splits;
-    float M = -INFINITY;
-    for (int sp = 0; sp < num_splits; ++sp) M = fmaxf(M, part_ml[(base + sp) * 2]);
-    const float U = M == -INFINITY ? 0.f : M;
-    float den = 0.f, acc = 0.f;
-    for (int sp = 0; sp < num_splits; ++sp) {
-      const float f = exp2f(part_ml[(base + sp) * 2] - U);
-      den += part_ml[(base + sp) * 2 + 1] * f;
-      acc += part_o[(base + sp) * D + dim] * f;
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  bool ok = true;
+  if (warp == 4) {
+    // ---- producer: tile t goes to stage t % S once the consumers have released that stage's previous tile
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int stage = t % SQ_STAGES;
+      if (t >= SQ_STAGES) ok = att_mbar_wait(&empty_bar[stage], ((t / SQ_STAGES) - 1) & 1, abort_flag, err, 3);
+      if (!ok) break;
+      tma_issue_tile(&kv_map, KV + stage * STAGE, &full_bar[stage], bt, T0 + t * BN, k_begin, k_end - 1, kvh, nkv, page_size,
+                     ps_shift, total_rows, lane);
     }
-    out[((size_t)tok * nq + head) * D + dim] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+  } else {
+    // ---- consumers: the query rows (row = token * G + head-in-group), then the tiles
+    for (int c = tid; c < 16 * KCH; c += 128) {
+      const int row = c / KCH, ch = c % KCH;
+      const bool valid = row < rows && n_tiles > 0;
+      const bf16* src = valid ? qkv + (size_t)(q0 + row / G) * row_stride + (size_t)(kvh * G + row % G) * D + ch * 8 : qkv;
+      cp_async16(Qs + row * DP + ch * 8, src, valid);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");           // the four consumer warps only
+    const int rowA = lane >> 2, rowB = rowA + 8;
+    const int pA = rowA < rows ? p_first + rowA / G : NO_ROW, pB = rowB < rows ? p_first + rowB / G : NO_ROW;
+    uint32_t qf[KB][4];
+    if (n_tiles > 0) load_q_frags(qf, Qs, lane);
+    for (int t = 0; t < n_tiles; ++t) {
+      const int stage = t % SQ_STAGES;
+      const bf16* Ks = KV + stage * STAGE;
+      const bf16* Vs = Ks + BN * D;
+      ok = att_mbar_wait(&full_bar[stage], (t / SQ_STAGES) & 1, abort_flag, err, 1);
+      if (!ok) break;
+      const int tile0 = T0 + t * BN;
+      const bool interior = tile0 >= k_begin && tile0 + BN - 1 <= min(p_first, k_end - 1) && (window == 0 || tile0 >= L - window);
+      if (interior)
+        warp_tile<2, false, true>(qf, Ks, Vs, warp * 16, tile0, k_begin, k_end - 1, pA, pB, window, scale_log2, m, l, o, lane);
+      else
+        warp_tile<2, true, true>(qf, Ks, Vs, warp * 16, tile0, k_begin, k_end - 1, pA, pB, window, scale_log2, m, l, o, lane);
+      __syncwarp();
+      if (lane == 0) att_mbar_arrive(&empty_bar[stage]);        // this warp is done with the stage
+    }
   }
-  if (tid == 0) counters[r * nkv + kvh] = 0;       // ready for the next launch
+  __syncthreads();                                              // every tile has been read; the stages are free
+  if (*abort_flag) {                                            // a wait gave up: let copies in flight land, then leave
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    return;
+  }
+  small_q_finish(reinterpret_cast<float*>(KV), m, l, o, rows, G, q0, kvh, r, split, num_splits, nq, nkv, out, part_o, part_ml,
+                 counters, &is_last);
 }
 
 // --------------------------------------------------------------------------------------------
@@ -645,7 +767,8 @@ static int att_launch(const CUtensorMap& map, int total_rows, int* err, const vo
                       int max_q_len, int num_splits, int run_small, int run_tiles, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_small_q_kernel<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_q_smem(TMA));
+    cudaError_t e = TMA ? cudaFuncSetAttribute(attn_small_q_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_q_smem(true))
+                        : cudaFuncSetAttribute(attn_small_q_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_q_smem(false));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_tile_kernel<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem(TMA));
     if (e != cudaSuccess) return -(int)e;
     configured = true;
@@ -655,9 +778,15 @@ static int att_launch(const CUtensorMap& map, int total_rows, int* err, const vo
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_tokens * nq * num_splits * D : nullptr;
     dim3 grid(num_splits, nkv, n_req);
-    int st = ifb_launch(attn_small_q_kernel<TMA>, grid, dim3(THREADS), small_q_smem(TMA), stream, map, total_rows, err,
-                        (const bf16*)qkv, row_stride, (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out,
-                        part_o, part_ml, counters, nq, nkv, page_size, scale_log2, window, num_splits);
+    int st;
+    if (TMA)
+      st = ifb_launch(attn_small_q_ws_kernel, grid, dim3(WS_THREADS), small_q_smem(true), stream, map, total_rows, err,
+                      (const bf16*)qkv, row_stride, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out, part_o, part_ml,
+                      counters, nq, nkv, page_size, scale_log2, window, num_splits);
+    else
+      st = ifb_launch(attn_small_q_kernel<false>, grid, dim3(THREADS), small_q_smem(false), stream, map, total_rows, err,
+                      (const bf16*)qkv, row_stride, (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, (bf16*)out,
+                      part_o, part_ml, counters, nq, nkv, page_size, scale_log2, window, num_splits);
     if (st) return st;
   }
   if (run_tiles) {
