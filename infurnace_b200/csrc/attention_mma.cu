@@ -582,7 +582,7 @@ attn_small_q_ws_kernel(const __grid_constant__ CUtensorMap kv_map, int total_row
 // tile kernel: grid (query tiles, kv heads, requests); a warp keeps floor(16/G) tokens x G heads
 // --------------------------------------------------------------------------------------------
 template <bool TMA>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, D <= 128 ? 3 : 1)      // three CTAs per SM where the accumulators allow
 attn_tile_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, int* __restrict__ err,
                  const bf16* __restrict__ qkv, int row_stride, const bf16* __restrict__ pages,
                  const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
@@ -595,7 +595,6 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, int
   constexpr int STAGE = TMA ? 2 * BN * D : 2 * BN * DP;
   const uint32_t raw = smem_u32(smem_raw);
   bf16* KV = reinterpret_cast<bf16*>(smem_raw + (TMA ? ((raw + 1023u) & ~1023u) - raw : 0u));
-  bf16* Qs = KV + 2 * STAGE;                                 // [64][DP]
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int kvh = blockIdx.y, r = blockIdx.z;
@@ -624,15 +623,6 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, int
     }
     __syncthreads();
   }
-  for (int c = tid; c < 64 * KCH; c += THREADS) {
-    const int row = c / KCH, ch = c % KCH;
-    const int w = row >> 4, rr = row & 15;
-    const int tok = t0 + w * tpw + rr / G;
-    const bool valid = rr < tpw * G && tok < t1;
-    const bf16* src = valid ? qkv + (size_t)(q0 + tok) * row_stride + (size_t)(kvh * G + rr % G) * D + ch * 8 : qkv;
-    cp_async16(Qs + row * DP + ch * 8, src, valid);
-  }
-  cp_async_commit();
   if (n_tiles > 0) {
     if (TMA) {
       if (warp == 0) tma_issue_tile(&kv_map, KV, &full_bar[0], bt, T0, lo, hi, kvh, nkv, page_size, ps_shift, total_rows, lane);
@@ -650,7 +640,20 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, int
   const int pA = (rowA < tpw * G && tokA < t1) ? p_first + tokA : NO_ROW;
   const int pB = (rowB < tpw * G && tokB < t1) ? p_first + tokB : NO_ROW;
   const int warp_hi = p_first + min(t1, t0 + (warp + 1) * tpw) - 1;        // last position this warp's rows see
+  // the warp's query rows as MMA fragments, straight from global memory (rows that do not exist are zeros)
   uint32_t qf[KB][4];
+  {
+    const bf16* qa = pA != NO_ROW ? qkv + (size_t)(q0 + tokA) * row_stride + (size_t)(kvh * G + rowA % G) * D : nullptr;
+    const bf16* qb = pB != NO_ROW ? qkv + (size_t)(q0 + tokB) * row_stride + (size_t)(kvh * G + rowB % G) * D : nullptr;
+    const int c0 = (lane & 3) << 1;
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb) {
+      qf[kb][0] = qa ? *reinterpret_cast<const uint32_t*>(qa + kb * 16 + c0) : 0u;
+      qf[kb][1] = qb ? *reinterpret_cast<const uint32_t*>(qb + kb * 16 + c0) : 0u;
+      qf[kb][2] = qa ? *reinterpret_cast<const uint32_t*>(qa + kb * 16 + 8 + c0) : 0u;
+      qf[kb][3] = qb ? *reinterpret_cast<const uint32_t*>(qb + kb * 16 + 8 + c0) : 0u;
+    }
+  }
   bool ok = true;
   for (int t = 0; t < n_tiles; ++t) {
     bf16* Ks = KV + (t & 1) * STAGE;
@@ -668,14 +671,12 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap kv_map, int total_rows, int
       }
     }
     if (TMA) {
-      if (t == 0) cp_async_wait<0>();
       ok = att_mbar_wait(&full_bar[t & 1], (t >> 1) & 1, abort_flag, err, 2);
     } else {
       if (t + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
     }
     __syncthreads();
     if (TMA && *abort_flag) { ok = false; break; }
-    if (t == 0) load_q_frags(qf, Qs + warp * 16 * DP, lane);
     const int tile0 = T0 + t * BN;
     if (tile0 <= warp_hi) {
       // every key of the tile is seen by every row of this warp: no masking
@@ -717,7 +718,7 @@ static size_t small_q_smem(bool tma) {
   return tma ? (size_t)(SQ_STAGES * 2 * BN * D + 16 * DP) * sizeof(bf16) + 1024 : (size_t)(SQ_STAGES * 2 * BN * DP + 16 * DP) * sizeof(bf16);
 }
 static size_t tile_smem(bool tma) {
-  return tma ? (size_t)(2 * 2 * BN * D + 64 * DP) * sizeof(bf16) + 1024 : (size_t)(2 * 2 * BN * DP + 64 * DP) * sizeof(bf16);
+  return tma ? (size_t)(2 * 2 * BN * D) * sizeof(bf16) + 1024 : (size_t)(2 * 2 * BN * DP) * sizeof(bf16);
 }
 
 typedef CUresult (*AttEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
