@@ -218,12 +218,19 @@ def run_ours(args):
         runner.use_graphs = False
     if args.mode == "prefill":
         toks = torch.randint(0, cfg.vocab_size, (PREFILL_TOKENS,)).tolist()
+        times = []
         for rep in range(max(1, steps)):
             runner.cache.add_request("p")
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
             runner.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])])
+            e.record()
             torch.cuda.synchronize()
             runner.cache.free_request("p")
-        print(json.dumps({"mode": "prefill", "tokens": PREFILL_TOKENS, "steps": max(1, steps)}))
+            times.append(s.elapsed_time(e))
+        print(json.dumps({"mode": "prefill", "tokens": PREFILL_TOKENS, "steps": max(1, steps),
+                          "ms_median": statistics.median(times), "ms_min": min(times)}))
         return 0
     sampler = Sampler(runner.rt.kernels, runner.rt.device)
     randomize_pages(runner)

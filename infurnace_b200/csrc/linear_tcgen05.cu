@@ -33,7 +33,7 @@ constexpr int G_TILE_BYTES = G_BM * G_BK * 2;   // 16 KB, same for an x tile and
 
 template <int EPI> struct GemmCfg {
   static constexpr int NB = EPI ? 2 : 1;                      // w tiles per stage
-  static constexpr int STAGES = EPI ? 4 : 3;                  // 4 x 48 KB, or 3 x 32 KB (two CTAs per SM)
+  static constexpr int STAGES = EPI ? 2 : 3;                  // 2 x 48 KB or 3 x 32 KB: two CTAs per SM either way
   static constexpr int STAGE_BYTES = (1 + NB) * G_TILE_BYTES;
   static constexpr int TMEM_COLS = NB * G_BN;                 // 128 or 256 columns of 32 bits
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
