@@ -1,0 +1,434 @@
+// Attention for prompts and long portions on the fifth-generation tensor cores, head size 128.
+//
+// A CTA takes 128 score rows of one key/value head: 128/G query tokens times the G query heads of the
+// group (row = token * G + head-in-group), and walks the request's keys in tiles of 128.  Per tile:
+//   S = Q K^T     tcgen05.mma, Q and K in shared memory (TMA, 128-byte swizzle), S in tensor memory;
+//   softmax       four warps, one thread per row: the row of S is read from tensor memory, masked,
+//                 exponentiated against the running maximum (float32), summed, and written back to
+//                 tensor memory as bfloat16 P; the running output is rescaled in tensor memory only
+//                 when a maximum grew by more than 2^8 (the kept maximum may lag by that much, which
+//                 float32 sums and bfloat16 P hold without loss);
+//   O += P V      tcgen05.mma with P as the A operand in tensor memory and V from shared memory as an
+//                 MN-major B operand (V is stored [key][dim], the dim running fastest).
+// Warp 0 issues the TMA loads (the query tile through a three-dimensional tensor map over the fused
+// qkv rows, key/value tiles page by page as in attention_mma.cu), one thread of warp 1 issues the MMAs,
+// warps 2-5 do the softmax and the final division and store.
+//
+// Requests are routed as in attention_mma.cu: this kernel takes those with more than 16 score rows,
+// the small-q kernel there takes the others.  Waits on barriers are bounded (TC_SPIN_LIMIT polls, then
+// a code in *err and the CTA's abort flag).
+#include "common.cuh"
+#include <cuda.h>
+#include <math.h>
+#include <string.h>
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+#if HEAD_DIM != 128
+#error "attention_tc.cu is written for head size 128"
+#endif
+
+typedef __nv_bfloat16 bf16;
+constexpr int D = 128;
+constexpr int ROWS = 128;                 // score rows per CTA (MMA M)
+constexpr int BK = 128;                   // keys per tile (MMA N of S, K of PV)
+constexpr int TC_THREADS = 192;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
+constexpr int HALF_BYTES = 128 * 128;     // a [128 rows][64 columns] bf16 half tile in the 128-byte swizzle: 16 KB
+constexpr int TILE_BYTES = 2 * HALF_BYTES;
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;             // K then V
+constexpr int TC_STAGES = 2;
+constexpr int SMEM_BYTES = TILE_BYTES /* Q */ + TC_STAGES * STAGE_BYTES + 1024 /* alignment */;
+// tensor memory columns (32-bit): S [0,128), O [128,256), P (bfloat16 pairs) [256,320)
+constexpr int COL_S = 0, COL_O = 128, COL_P = 256, TMEM_COLS = 512;
+constexpr int NO_ROW = -1000000000;
+
+__device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(tc_smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+  for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+    if (tc_mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(err, code);
+  return false;
+}
+__device__ __forceinline__ void tc_tma_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(tc_smem_u32(smem)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_tma_3d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+               ::"r"(tc_smem_u32(smem)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// D[tmem] (+)= A[tmem] B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ float tc_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t tc_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// K-major operand (rows of 128 bytes = 64 k, groups of 8 rows 1024 bytes apart), 128-byte swizzle: Q and K tiles.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand, 128-byte swizzle: the V tile [key][dim] as B = [dim (N)][key (K)].  64 dims (128 bytes) are one
+// swizzle row; the next 64 dims lie HALF_BYTES further (leading byte offset); 8 keys are 1024 bytes (stride byte offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)(HALF_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// float32 accumulator, bfloat16 A and B, M = 128, N = 128; B K-major for S = Q K^T, MN-major for O += P V.
+constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+constexpr uint32_t IDESC_PV = IDESC_S | (1u << 16);
+
+__global__ void __launch_bounds__(TC_THREADS)
+attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, int total_rows,
+                    int* __restrict__ err, const int* __restrict__ block_tables, int bt_stride,
+                    const int* __restrict__ cu_q, const int* __restrict__ seq_lens, bf16* __restrict__ out, int nq, int nkv,
+                    int page_size, float scale_log2, int window) {
+  extern __shared__ unsigned char tc_smem_raw[];
+  __shared__ uint64_t q_full, kv_full[TC_STAGES], kv_empty[TC_STAGES], s_full, p_ready, o_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const uint32_t raw = tc_smem_u32(tc_smem_raw);
+  unsigned char* smem = tc_smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  unsigned char* Qs = smem;                                  // [2 halves][128 rows][128 bytes]
+  unsigned char* KV = smem + TILE_BYTES;                     // TC_STAGES x (K tile, V tile)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.y, r = blockIdx.z;
+  const int G = nq / nkv;
+  const int q0 = cu_q[r], q_len = cu_q[r + 1] - q0, L = seq_lens[r];
+  if (q_len * G <= 16) return;                               // the small-q kernel's request
+  const int tpc = ROWS / G;                                  // tokens per CTA
+  const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * tpc;    // longest key ranges first
+  if (t0 >= q_len) return;
+  const int t1 = min(q_len, t0 + tpc);
+  const int p_first = L - q_len;
+  const int lo = window > 0 ? max(0, p_first + t0 - window + 1) : 0, hi = p_first + t1 - 1;
+  const int T0 = (lo / BK) * BK;
+  const int n_tiles = hi >= lo ? (hi + 1 - T0 + BK - 1) / BK : 0;
+  const int* bt = block_tables + (size_t)r * bt_stride;
+  const int ps_shift = __ffs(page_size) - 1;
+
+  if (threadIdx.x == 0) {
+    tc_mbar_init(&q_full, 1);
+    for (int s = 0; s < TC_STAGES; ++s) { tc_mbar_init(&kv_full[s], 1); tc_mbar_init(&kv_empty[s], 1); }
+    tc_mbar_init(&s_full, 1);
+    tc_mbar_init(&p_ready, 128);
+    tc_mbar_init(&o_done, 1);
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- producer
+    if (lane == 0) {
+      tc_mbar_expect_tx(&q_full, TILE_BYTES);
+      tc_tma_3d(Qs, &q_map, &q_full, 0, kvh * G, q0 + t0);
+      tc_tma_3d(Qs + HALF_BYTES, &q_map, &q_full, 64, kvh * G, q0 + t0);
+    }
+    const int ppt = BK >> ps_shift;                          // pages per tile: 8, 4 or 2
+    const int n_ops = ppt * 2 * 2;                           // x 2 halves x (K, V): at most 32
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j % TC_STAGES;
+      if (j >= TC_STAGES) ok = tc_mbar_wait(&kv_empty[st], ((j / TC_STAGES) - 1) & 1, abort_flag, err, 11);
+      if (!ok) break;
+      if (lane == 0) tc_mbar_expect_tx(&kv_full[st], STAGE_BYTES);
+      __syncwarp();
+      if (lane < n_ops) {
+        const int kv = lane / (ppt * 2), rem = lane % (ppt * 2), pg = rem >> 1, half = rem & 1;
+        const int key0 = T0 + j * BK + pg * page_size;
+        int y = total_rows;                                  // beyond the tensor: zeros
+        if (key0 <= hi && key0 + page_size - 1 >= lo) y = ((bt[key0 >> ps_shift] * 2 + kv) * nkv + kvh) * page_size;
+        tc_tma_2d(KV + st * STAGE_BYTES + kv * TILE_BYTES + half * HALF_BYTES + pg * page_size * 128, &kv_map, &kv_full[st],
+                  half * 64, y);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      bool ok = tc_mbar_wait(&q_full, 0, abort_flag, err, 12);
+      const uint32_t q_addr = tc_smem_u32(Qs);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % TC_STAGES;
+        ok = tc_mbar_wait(&kv_full[st], (j / TC_STAGES) & 1, abort_flag, err, 13);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t k_addr = tc_smem_u32(KV + st * STAGE_BYTES), v_addr = k_addr + TILE_BYTES;
+        // S = Q K^T: 8 steps of 16 along the head size, 4 per 64-column half
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          tc_mma_ss(tmem + COL_S, desc_k_major(q_addr + off), desc_k_major(k_addr + off), IDESC_S, ks != 0);
+        }
+        tc_commit(&s_full);
+        ok = tc_mbar_wait(&p_ready, j & 1, abort_flag, err, 14);
+        if (!ok) break;
+        tc_fence_after();
+        // O += P V: 8 steps of 16 keys; P at 8 columns (16 bfloat16) per step, V 2048 bytes (16 key rows) per step
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          tc_mma_ts(tmem + COL_O, tmem + COL_P + ks * 8, desc_mn_major(v_addr + ks * 2048), IDESC_PV, (j | ks) != 0);
+        tc_commit(&kv_empty[st]);
+        tc_commit(&o_done);
+      }
+    }
+  } else {
+    // ---------------- softmax, one thread per row
+    const int qd = warp & 3;                                 // this warp's quarter of the 128 lanes
+    const int row = qd * 32 + lane;
+    const int tok = t0 + row / G;
+    const int p = tok < t1 ? p_first + tok : NO_ROW;
+    const int row_lo = window > 0 ? p - window + 1 : 0;
+    const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      ok = __all_sync(0xffffffffu, tc_mbar_wait(&s_full, j & 1, abort_flag, err, 15)) != 0;    // warp-uniform
+      if (!ok) break;
+      tc_fence_after();
+      const int key0 = T0 + j * BK;
+      // pass 1: the row's maximum over the visible keys of the tile
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tc_ld32(lane_addr + COL_S + c * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key0 + c * 32 + i;
+          const bool vis = key <= p && key >= row_lo && key >= lo && key <= hi;
+          if (vis) mx = fmaxf(mx, __uint_as_float(v[i]) * scale_log2);
+        }
+      }
+      // keep the old reference maximum unless the new one is more than 2^8 above it (warp-uniform decision,
+      // since the tensor-memory loads and stores of the rescaling are warp-wide)
+      const float m_new = fmaxf(m_used, mx);
+      const bool grow = m_new > m_used + 8.f;
+      const bool any_grow = __any_sync(0xffffffffu, grow) != 0;
+      float factor = 1.f;
+      if (any_grow && grow) {
+        factor = m_used == -INFINITY ? 0.f : tc_exp2(m_used - m_new);
+        m_used = m_new;
+      }
+      const float ref = m_used == -INFINITY ? 0.f : m_used;
+      if (j > 0) {
+        // the previous tile's P V must have landed in O before O is rescaled or P is overwritten
+        ok = __all_sync(0xffffffffu, tc_mbar_wait(&o_done, (j - 1) & 1, abort_flag, err, 16)) != 0;
+        if (!ok) break;
+        tc_fence_after();
+        if (any_grow) {
+          l *= factor;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tc_ld32(lane_addr + COL_O + c * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
+            tc_st32(lane_addr + COL_O + c * 32, v);
+          }
+        }
+      }
+      // pass 2: p = 2^(s - ref), the row sum, and P as bfloat16 pairs
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32], pk[16];
+        tc_ld32(lane_addr + COL_S + c * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int key = key0 + c * 32 + i;
+          const bool v0 = key <= p && key >= row_lo && key >= lo && key <= hi;
+          const bool v1 = key + 1 <= p && key + 1 >= row_lo && key + 1 >= lo && key + 1 <= hi;
+          const float e0 = v0 ? tc_exp2(__uint_as_float(v[i]) * scale_log2 - ref) : 0.f;
+          const float e1 = v1 ? tc_exp2(__uint_as_float(v[i + 1]) * scale_log2 - ref) : 0.f;
+          l += e0 + e1;
+          pk[i >> 1] = tc_pack(e0, e1);
+        }
+        tc_st16(lane_addr + COL_P + c * 16, pk);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      tc_mbar_arrive(&p_ready);
+    }
+    if (ok && n_tiles > 0) {
+      ok = __all_sync(0xffffffffu, tc_mbar_wait(&o_done, (n_tiles - 1) & 1, abort_flag, err, 17)) != 0;
+      if (ok) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* dst = p != NO_ROW ? out + ((size_t)(q0 + tok) * nq + kvh * G + row % G) * D : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tc_ld32(lane_addr + COL_O + c * 32, v);
+          tc_wait_ld();
+          if (dst) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 pk;
+              pk.x = tc_pack(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+              pk.y = tc_pack(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+              pk.z = tc_pack(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+              pk.w = tc_pack(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + i) = pk;
+            }
+          }
+        }
+      }
+    } else if (n_tiles == 0 && p != NO_ROW) {
+      bf16* dst = out + ((size_t)(q0 + tok) * nq + kvh * G + row % G) * D;
+      for (int i = 0; i < D; ++i) dst[i] = __float2bfloat16_rn(0.f);
+    }
+  }
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+typedef CUresult (*TcEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TcEncodeTiledFn tc_encode() {
+  static TcEncodeTiledFn enc = nullptr;
+  if (!enc) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      enc = (TcEncodeTiledFn)fn;
+  }
+  return enc;
+}
+
+// qkv [n_tokens, row_stride] bfloat16 (the q heads are the first nq * 128 columns), pages [num_pages, 2, nkv, page_size, 128],
+// out [n_tokens, nq * 128].  Takes the requests with q_len * (nq / nkv) > 16.  The group size nq / nkv must divide 128 and
+// page_size must be 16, 32 or 64.  err: a device int that stays 0 unless a bounded wait gave up.
+IFB_EXPORT int ifb_attention_tc(const void* qkv, int row_stride, const void* pages, long long num_pages, const int* block_tables,
+                                int bt_stride, const int* cu_q, const int* seq_lens, void* out, int* err, int n_tokens, int n_req,
+                                int nq, int nkv, int d, int page_size, float scale, int window, int max_q_len,
+                                cudaStream_t stream) {
+  if (n_tokens <= 0 || n_req <= 0) return IFB_OK;
+  if (d != D) return IFB_ERR_SIZE;
+  if (nkv < 1 || nq % nkv || window < 0 || !err) return IFB_ERR_ARG;
+  const int G = nq / nkv;
+  if (G > ROWS || ROWS % G) return IFB_ERR_SIZE;
+  if (page_size != 16 && page_size != 32 && page_size != 64) return IFB_ERR_SIZE;
+  if (row_stride % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)pages & 127) || ((uintptr_t)out & 15)) return IFB_ERR_ALIGN;
+  const long long rows = num_pages * 2 * nkv * page_size;
+  if (rows >= 0x7fffffffLL || n_req > 65535 || nkv > 65535) return IFB_ERR_SIZE;
+  TcEncodeTiledFn enc = tc_encode();
+  if (!enc) return IFB_ERR_ARG;
+  CUtensorMap q_map, kv_map;
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nq, (cuuint64_t)n_tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)row_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(ROWS / G)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (enc(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(qkv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return IFB_ERR_ARG;
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&kv_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return IFB_ERR_ARG;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_tile_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return -(int)e;
+    configured = true;
+  }
+  const int tpc = ROWS / G;
+  dim3 grid((max_q_len + tpc - 1) / tpc, nkv, n_req);
+  attn_tile_tc_kernel<<<grid, TC_THREADS, SMEM_BYTES, stream>>>(q_map, kv_map, (int)rows, err, block_tables, bt_stride, cu_q, seq_lens,
+                                                                (bf16*)out, nq, nkv, page_size, scale * 1.4426950408889634f, window);
+  return ifb_launch_status();
+}

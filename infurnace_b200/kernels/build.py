@@ -33,6 +33,7 @@ LIBRARIES: Dict[str, tuple] = {
     "linear_tcgen05": (["linear_tcgen05.cu"], []),
     # the few-rows product with its scratch inside the library, for callers that must not allocate
     "linear_skinny_static": (["linear_skinny_static.cu"], []),
+    "attention_tc": (["attention_tc.cu"], []),            # head size 128
     # compiled once per head size: defines={"HEAD_DIM": d}
     "attention_mma": (["attention_mma.cu"], []),
 }
@@ -163,6 +164,6 @@ def load_library(name: str, defines: Optional[Dict[str, object]] = None, progres
 def build_all(progress=None) -> List[str]:
     """Compile every library (used by the build check; needs no GPU)."""
     from concurrent.futures import ThreadPoolExecutor
-    jobs = [("core", None), ("linear_tcgen05", None), ("linear_skinny_static", None)] + DEFAULT_VARIANTS
+    jobs = [("core", None), ("linear_tcgen05", None), ("linear_skinny_static", None), ("attention_tc", None)] + DEFAULT_VARIANTS
     with ThreadPoolExecutor(max_workers=4) as pool:
         return list(pool.map(lambda j: compile_library(j[0], j[1], progress), jobs))

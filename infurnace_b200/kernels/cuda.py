@@ -82,6 +82,8 @@ class CudaKernels:
         self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
         self._dev_err = None           # device int: non-zero after a bounded barrier wait in a kernel gave up
         self.attention_tma = True      # keys and values by TMA where the sizes allow (else 16-byte async copies)
+        self.attention_tc = True       # prompts on tcgen05 where the sizes allow (head size 128, pages of 16/32/64)
+        self._attn_tc = None
         self._err_armed = False
         self.tc_min_rows = 65
         self._attn_mma = {}        # head size -> library
@@ -262,6 +264,23 @@ class CudaKernels:
             qkv.data_ptr(), _code(qkv), qkv.stride(0), kv_pages.data_ptr(), block_tables.data_ptr(),
             block_tables.stride(0), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), n, r, num_heads,
             num_kv_heads, head_dim, kv_pages.shape[3], float(scale), int(window), self._stream()), "paged_attention")
+
+    def _attention_tc(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out, scale,
+                      window, max_q_len, n, r):
+        if self._attn_tc is None:
+            self._attn_tc = load_library("attention_tc", progress=self._progress)
+            self._attn_tc.ifb_attention_tc.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+                                                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                       c_int, c_int, c_void_p]
+        if self._dev_err is None:
+            self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self._err_armed = True
+        self.launches += 1
+        _check(self._attn_tc.ifb_attention_tc(
+            qkv.data_ptr(), qkv.stride(0), kv_pages.data_ptr(), kv_pages.shape[0], block_tables.data_ptr(),
+            block_tables.stride(0), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), self._dev_err.data_ptr(), n, r,
+            num_heads, num_kv_heads, head_dim, kv_pages.shape[3], float(scale), int(window), int(max_q_len), self._stream()),
+            "paged_attention")
 
     def attention_library(self, head_dim):
         lib = self._attn_mma.get(head_dim)

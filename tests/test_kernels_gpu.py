@@ -283,3 +283,24 @@ def test_linear_gemv(K, od, n, o, k, epilogue):
     K._linear_gemv(x.cuda(), w.cuda(), out, n, o, k, 1 if epilogue == "silu_gate" else 0)
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2 if od == torch.bfloat16 else 2e-4,
                                atol=2e-3 if od == torch.bfloat16 else 1e-4)
+
+
+@pytest.mark.parametrize("nq,nkv,ps,window", [(16, 8, 16, 0), (4, 4, 16, 0), (8, 2, 32, 0), (16, 2, 64, 0), (16, 1, 16, 0),
+                                              (16, 8, 16, 100), (2, 1, 32, 37)])
+def test_attention_on_tcgen05(K, nq, nkv, ps, window):
+    """Prompts and long portions of head size 128 on tcgen05 (S and P in tensor memory), beside
+    decoded tokens that the small-q kernel takes in the same call: every group size that divides
+    128, every page size the TMA path takes, with and without a window, portions that start deep
+    inside a context and tiles that hang over the ends."""
+    dtype, d = torch.bfloat16, 128
+    q_lens, seq_lens = [200, 1, 130, 33, 1], [260, 50, 130, 500, 129]
+    qkv, kv, bt, cu, sl = _attention_case(dtype, nq, nkv, d, ps, window, q_lens, seq_lens, 21, spike=(window == 0))
+    n = qkv.shape[0]
+    ref = torch.empty((n, nq * d), dtype=dtype)
+    REF.paged_attention(qkv, nq, nkv, d, kv, bt, cu, sl, ref, d ** -0.5, window, max(q_lens), max(seq_lens))
+    out = torch.full((n, nq * d), float("nan"), dtype=dtype, device="cuda")
+    assert K.attention_tc
+    K.paged_attention(qkv.cuda(), nq, nkv, d, kv.cuda(), bt.cuda(), cu.cuda(), sl.cuda(), out, d ** -0.5, window,
+                      max(q_lens), max(seq_lens))
+    K.check_device_errors()
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2, atol=1.6e-2)
