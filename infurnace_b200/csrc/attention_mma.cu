@@ -26,8 +26,8 @@
 // on the barriers are bounded: after ATT_SPIN_LIMIT polls a thread records a code in `*err`, raises
 // the CTA's abort flag and the CTA leaves.  Other sizes take the cp.async path: 16-byte copies by all
 // threads into padded rows.
-#include "common.cuh"
 #include <cuda.h>
+#include "common.cuh"
 #include <math.h>
 #include <string.h>
 
@@ -721,37 +721,13 @@ static size_t tile_smem(bool tma) {
   return tma ? (size_t)(2 * 2 * BN * D) * sizeof(bf16) + 1024 : (size_t)(2 * 2 * BN * DP) * sizeof(bf16);
 }
 
-typedef CUresult (*AttEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 // The pool [pages, 2, kv_heads, page_size, D] as a matrix [rows, D] with boxes of page_size rows x 64 columns in
-// the 128-byte swizzle.  Maps are kept by (address, rows, page size): a model has one pool per layer.
+// the 128-byte swizzle.
 static int kv_tensor_map(CUtensorMap* out, const void* pages, long long rows, int page_size) {
-  struct Entry { const void* p; long long rows; int ps; CUtensorMap map; };
-  static Entry cache[512];
-  static int used = 0;
-  for (int i = 0; i < used; ++i)
-    if (cache[i].p == pages && cache[i].rows == rows && cache[i].ps == page_size) { *out = cache[i].map; return IFB_OK; }
-  static AttEncodeTiledFn enc = nullptr;
-  if (!enc) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-      return IFB_ERR_ARG;
-    enc = (AttEncodeTiledFn)fn;
-  }
-  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(bf16)};
-  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
-  cuuint32_t estr[2] = {1, 1};
-  CUtensorMap m;
-  if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return IFB_ERR_ARG;
-  if (used < 512) { cache[used].p = pages; cache[used].rows = rows; cache[used].ps = page_size; cache[used].map = m; ++used; }
-  *out = m;
-  return IFB_OK;
+  const unsigned long long dims[2] = {(unsigned long long)D, (unsigned long long)rows};
+  const unsigned long long strides[1] = {(unsigned long long)D * sizeof(bf16)};
+  const unsigned box[2] = {64, (unsigned)page_size};
+  return ifb_tensor_map_bf16(out, pages, 2, dims, strides, box);
 }
 
 IFB_EXPORT int ifb_attention_mma_head_dim() { return D; }

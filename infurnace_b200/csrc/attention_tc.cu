@@ -12,13 +12,15 @@
 //                 MN-major B operand (V is stored [key][dim], the dim running fastest).
 // Warp 0 issues the TMA loads (the query tile through a three-dimensional tensor map over the fused
 // qkv rows, key/value tiles page by page as in attention_mma.cu), one thread of warp 1 issues the MMAs,
-// warps 2-5 do the softmax and the final division and store.
+// warps 2-5 do the softmax and the final division and store.  K and V have one buffer each with barriers
+// of their own: the next K tile is fetched while this tile's softmax runs, the next V tile while the
+// next scores are formed.  Two CTAs share an SM, so one's softmax runs beside the other's MMAs.
 //
 // Requests are routed as in attention_mma.cu: this kernel takes those with more than 16 score rows,
 // the small-q kernel there takes the others.  Waits on barriers are bounded (TC_SPIN_LIMIT polls, then
 // a code in *err and the CTA's abort flag).
-#include "common.cuh"
 #include <cuda.h>
+#include "common.cuh"
 #include <math.h>
 #include <string.h>
 
@@ -37,11 +39,10 @@ constexpr int TC_THREADS = 192;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 constexpr int HALF_BYTES = 128 * 128;     // a [128 rows][64 columns] bf16 half tile in the 128-byte swizzle: 16 KB
 constexpr int TILE_BYTES = 2 * HALF_BYTES;
-constexpr int STAGE_BYTES = 2 * TILE_BYTES;             // K then V
-constexpr int TC_STAGES = 2;
-constexpr int SMEM_BYTES = TILE_BYTES /* Q */ + TC_STAGES * STAGE_BYTES + 1024 /* alignment */;
-// tensor memory columns (32-bit): S [0,128), O [128,256), P (bfloat16 pairs) [256,320)
-constexpr int COL_S = 0, COL_O = 128, COL_P = 256, TMEM_COLS = 512;
+constexpr int SMEM_BYTES = 3 * TILE_BYTES /* Q, K, V */ + 1024 /* alignment */;       // 97 KB: two CTAs per SM
+// tensor memory columns (32-bit): S [0,128) with P (bfloat16 pairs) written over its first 64 as the row is
+// consumed, O [128,256).  256 columns per CTA: two CTAs share an SM's 512.
+constexpr int COL_S = 0, COL_P = 0, COL_O = 128, TMEM_COLS = 256;
 constexpr int NO_ROW = -1000000000;
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -145,20 +146,21 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 constexpr uint32_t IDESC_PV = IDESC_S | (1u << 16);
 
-__global__ void __launch_bounds__(TC_THREADS)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, int total_rows,
                     int* __restrict__ err, const int* __restrict__ block_tables, int bt_stride,
                     const int* __restrict__ cu_q, const int* __restrict__ seq_lens, bf16* __restrict__ out, int nq, int nkv,
                     int page_size, float scale_log2, int window) {
   extern __shared__ unsigned char tc_smem_raw[];
-  __shared__ uint64_t q_full, kv_full[TC_STAGES], kv_empty[TC_STAGES], s_full, p_ready, o_done;
+  __shared__ uint64_t q_full, k_full, v_full, k_empty, v_empty, s_full, p_ready, o_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
   const uint32_t raw = tc_smem_u32(tc_smem_raw);
   unsigned char* smem = tc_smem_raw + (((raw + 1023u) & ~1023u) - raw);
   unsigned char* Qs = smem;                                  // [2 halves][128 rows][128 bytes]
-  unsigned char* KV = smem + TILE_BYTES;                     // TC_STAGES x (K tile, V tile)
+  unsigned char* Ks = smem + TILE_BYTES;                     // K tile, same layout
+  unsigned char* Vs = smem + 2 * TILE_BYTES;                 // V tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.y, r = blockIdx.z;
   const int G = nq / nkv;
@@ -177,7 +179,7 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 
   if (threadIdx.x == 0) {
     tc_mbar_init(&q_full, 1);
-    for (int s = 0; s < TC_STAGES; ++s) { tc_mbar_init(&kv_full[s], 1); tc_mbar_init(&kv_empty[s], 1); }
+    tc_mbar_init(&k_full, 1); tc_mbar_init(&v_full, 1); tc_mbar_init(&k_empty, 1); tc_mbar_init(&v_empty, 1);
     tc_mbar_init(&s_full, 1);
     tc_mbar_init(&p_ready, 128);
     tc_mbar_init(&o_done, 1);
@@ -202,21 +204,23 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       tc_tma_3d(Qs + HALF_BYTES, &q_map, &q_full, 64, kvh * G, q0 + t0);
     }
     const int ppt = BK >> ps_shift;                          // pages per tile: 8, 4 or 2
-    const int n_ops = ppt * 2 * 2;                           // x 2 halves x (K, V): at most 32
+    const int n_ops = ppt * 2;                               // x 2 halves: at most 16 per tile
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int st = j % TC_STAGES;
-      if (j >= TC_STAGES) ok = tc_mbar_wait(&kv_empty[st], ((j / TC_STAGES) - 1) & 1, abort_flag, err, 11);
-      if (!ok) break;
-      if (lane == 0) tc_mbar_expect_tx(&kv_full[st], STAGE_BYTES);
-      __syncwarp();
-      if (lane < n_ops) {
-        const int kv = lane / (ppt * 2), rem = lane % (ppt * 2), pg = rem >> 1, half = rem & 1;
-        const int key0 = T0 + j * BK + pg * page_size;
-        int y = total_rows;                                  // beyond the tensor: zeros
-        if (key0 <= hi && key0 + page_size - 1 >= lo) y = ((bt[key0 >> ps_shift] * 2 + kv) * nkv + kvh) * page_size;
-        tc_tma_2d(KV + st * STAGE_BYTES + kv * TILE_BYTES + half * HALF_BYTES + pg * page_size * 128, &kv_map, &kv_full[st],
-                  half * 64, y);
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {                       // the K tile, then the V tile
+        uint64_t* full = kv ? &v_full : &k_full;
+        if (j > 0) ok = tc_mbar_wait(kv ? &v_empty : &k_empty, (j - 1) & 1, abort_flag, err, 11);
+        if (!ok) break;
+        if (lane == 0) tc_mbar_expect_tx(full, TILE_BYTES);
+        __syncwarp();
+        if (lane < n_ops) {
+          const int pg = lane >> 1, half = lane & 1;
+          const int key0 = T0 + j * BK + pg * page_size;
+          int y = total_rows;                                // beyond the tensor: zeros
+          if (key0 <= hi && key0 + page_size - 1 >= lo) y = ((bt[key0 >> ps_shift] * 2 + kv) * nkv + kvh) * page_size;
+          tc_tma_2d((kv ? Vs : Ks) + half * HALF_BYTES + pg * page_size * 128, &kv_map, full, half * 64, y);
+        }
       }
     }
   } else if (warp == 1) {
@@ -224,27 +228,28 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     if (lane == 0) {
       bool ok = tc_mbar_wait(&q_full, 0, abort_flag, err, 12);
       const uint32_t q_addr = tc_smem_u32(Qs);
+      const uint32_t k_addr = tc_smem_u32(Ks), v_addr = tc_smem_u32(Vs);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j % TC_STAGES;
-        ok = tc_mbar_wait(&kv_full[st], (j / TC_STAGES) & 1, abort_flag, err, 13);
+        ok = tc_mbar_wait(&k_full, j & 1, abort_flag, err, 13);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t k_addr = tc_smem_u32(KV + st * STAGE_BYTES), v_addr = k_addr + TILE_BYTES;
-        // S = Q K^T: 8 steps of 16 along the head size, 4 per 64-column half
+        // S = Q K^T: 8 steps of 16 along the head size, 4 per 64-column half.  (S lies where the previous tile's P
+        // lay; the tensor core takes its operations in the order they were issued, the previous P V first.)
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
           tc_mma_ss(tmem + COL_S, desc_k_major(q_addr + off), desc_k_major(k_addr + off), IDESC_S, ks != 0);
         }
+        tc_commit(&k_empty);
         tc_commit(&s_full);
-        ok = tc_mbar_wait(&p_ready, j & 1, abort_flag, err, 14);
+        ok = tc_mbar_wait(&p_ready, j & 1, abort_flag, err, 14) && tc_mbar_wait(&v_full, j & 1, abort_flag, err, 18);
         if (!ok) break;
         tc_fence_after();
         // O += P V: 8 steps of 16 keys; P at 8 columns (16 bfloat16) per step, V 2048 bytes (16 key rows) per step
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           tc_mma_ts(tmem + COL_O, tmem + COL_P + ks * 8, desc_mn_major(v_addr + ks * 2048), IDESC_PV, (j | ks) != 0);
-        tc_commit(&kv_empty[st]);
+        tc_commit(&v_empty);
         tc_commit(&o_done);
       }
     }
@@ -263,6 +268,9 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       const int key0 = T0 + j * BK;
+      // a tile every key of which every row of the CTA sees needs no masking (rows past the request's tokens are
+      // computed like the others and never stored)
+      const bool interior = key0 >= lo && key0 + BK - 1 <= min(hi, p_first + t0) && (window == 0 || key0 >= hi - window + 1);
       // pass 1: the row's maximum over the visible keys of the tile
       float mx = -INFINITY;
 #pragma unroll 1
@@ -270,13 +278,19 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         uint32_t v[32];
         tc_ld32(lane_addr + COL_S + c * 32, v);
         tc_wait_ld();
+        if (interior) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c * 32 + i;
-          const bool vis = key <= p && key >= row_lo && key >= lo && key <= hi;
-          if (vis) mx = fmaxf(mx, __uint_as_float(v[i]) * scale_log2);
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            const bool vis = key <= p && key >= row_lo && key >= lo && key <= hi;
+            if (vis) mx = fmaxf(mx, __uint_as_float(v[i]));
+          }
         }
       }
+      mx *= scale_log2;                                        // the scale is positive: the maximum commutes with it
       // keep the old reference maximum unless the new one is more than 2^8 above it (warp-uniform decision,
       // since the tensor-memory loads and stores of the rescaling are warp-wide)
       const float m_new = fmaxf(m_used, mx);
@@ -306,21 +320,32 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           }
         }
       }
-      // pass 2: p = 2^(s - ref), the row sum, and P as bfloat16 pairs
+      // pass 2: p = 2^(s - ref), the row sum, and P as bfloat16 pairs.  P goes over the part of S already read: the
+      // 16 columns of chunk c lie below column 32 (c + 1).
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32], pk[16];
         tc_ld32(lane_addr + COL_S + c * 32, v);
         tc_wait_ld();
+        if (interior) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int key = key0 + c * 32 + i;
-          const bool v0 = key <= p && key >= row_lo && key >= lo && key <= hi;
-          const bool v1 = key + 1 <= p && key + 1 >= row_lo && key + 1 >= lo && key + 1 <= hi;
-          const float e0 = v0 ? tc_exp2(__uint_as_float(v[i]) * scale_log2 - ref) : 0.f;
-          const float e1 = v1 ? tc_exp2(__uint_as_float(v[i + 1]) * scale_log2 - ref) : 0.f;
-          l += e0 + e1;
-          pk[i >> 1] = tc_pack(e0, e1);
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = tc_exp2(fmaf(__uint_as_float(v[i]), scale_log2, -ref));
+            const float e1 = tc_exp2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -ref));
+            l += e0 + e1;
+            pk[i >> 1] = tc_pack(e0, e1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int key = key0 + c * 32 + i;
+            const bool v0 = key <= p && key >= row_lo && key >= lo && key <= hi;
+            const bool v1 = key + 1 <= p && key + 1 >= row_lo && key + 1 >= lo && key + 1 <= hi;
+            const float e0 = v0 ? tc_exp2(fmaf(__uint_as_float(v[i]), scale_log2, -ref)) : 0.f;
+            const float e1 = v1 ? tc_exp2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -ref)) : 0.f;
+            l += e0 + e1;
+            pk[i >> 1] = tc_pack(e0, e1);
+          }
         }
         tc_st16(lane_addr + COL_P + c * 16, pk);
       }
@@ -369,20 +394,6 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------------------------
-typedef CUresult (*TcEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static TcEncodeTiledFn tc_encode() {
-  static TcEncodeTiledFn enc = nullptr;
-  if (!enc) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      enc = (TcEncodeTiledFn)fn;
-  }
-  return enc;
-}
-
 // qkv [n_tokens, row_stride] bfloat16 (the q heads are the first nq * 128 columns), pages [num_pages, 2, nkv, page_size, 128],
 // out [n_tokens, nq * 128].  Takes the requests with q_len * (nq / nkv) > 16.  The group size nq / nkv must divide 128 and
 // page_size must be 16, 32 or 64.  err: a device int that stays 0 unless a bounded wait gave up.
@@ -399,26 +410,18 @@ IFB_EXPORT int ifb_attention_tc(const void* qkv, int row_stride, const void* pag
   if (row_stride % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)pages & 127) || ((uintptr_t)out & 15)) return IFB_ERR_ALIGN;
   const long long rows = num_pages * 2 * nkv * page_size;
   if (rows >= 0x7fffffffLL || n_req > 65535 || nkv > 65535) return IFB_ERR_SIZE;
-  TcEncodeTiledFn enc = tc_encode();
-  if (!enc) return IFB_ERR_ARG;
   CUtensorMap q_map, kv_map;
   {
-    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nq, (cuuint64_t)n_tokens};
-    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)row_stride * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(ROWS / G)};
-    cuuint32_t estr[3] = {1, 1, 1};
-    if (enc(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(qkv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return IFB_ERR_ARG;
+    const unsigned long long dims[3] = {(unsigned long long)D, (unsigned long long)nq, (unsigned long long)n_tokens};
+    const unsigned long long strides[2] = {(unsigned long long)D * 2, (unsigned long long)row_stride * 2};
+    const unsigned box[3] = {64, (unsigned)G, (unsigned)(ROWS / G)};
+    if (ifb_tensor_map_bf16(&q_map, qkv, 3, dims, strides, box)) return IFB_ERR_ARG;
   }
   {
-    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)page_size};
-    cuuint32_t estr[2] = {1, 1};
-    if (enc(&kv_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return IFB_ERR_ARG;
+    const unsigned long long dims[2] = {(unsigned long long)D, (unsigned long long)rows};
+    const unsigned long long strides[1] = {(unsigned long long)D * 2};
+    const unsigned box[2] = {64, (unsigned)page_size};
+    if (ifb_tensor_map_bf16(&kv_map, pages, 2, dims, strides, box)) return IFB_ERR_ARG;
   }
   static bool configured = false;
   if (!configured) {

@@ -60,6 +60,65 @@ static inline int ifb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   return IFB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// A small host-side store of encoded tensor maps, for files that include <cuda.h> before this header.
+// Encoding a map is a driver call of several microseconds; a step encodes the same few hundred maps
+// (weights, activation buffers and page pools keep their addresses), so they are kept by their key.
+#ifdef CUDA_VERSION
+struct IfbMapKey {
+  const void* ptr;
+  unsigned long long dims[3], strides[2];
+  unsigned box[3];
+  int rank;
+  bool operator==(const IfbMapKey& o) const {
+    return ptr == o.ptr && rank == o.rank && dims[0] == o.dims[0] && dims[1] == o.dims[1] && dims[2] == o.dims[2] &&
+           strides[0] == o.strides[0] && strides[1] == o.strides[1] && box[0] == o.box[0] && box[1] == o.box[1] && box[2] == o.box[2];
+  }
+};
+typedef CUresult (*IfbEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// A bfloat16 tensor of rank 2 or 3 (dims and box innermost first, strides in bytes for dims 1..rank-1), 128-byte
+// swizzle, zeros outside.  Returns IFB_OK or IFB_ERR_ARG.
+static inline int ifb_tensor_map_bf16(CUtensorMap* out, const void* ptr, int rank, const unsigned long long* dims,
+                                      const unsigned long long* strides, const unsigned* box) {
+  constexpr int SLOTS = 4096;
+  static IfbMapKey keys[SLOTS];
+  static CUtensorMap maps[SLOTS];
+  static bool used[SLOTS];
+  static IfbEncodeTiledFn enc = nullptr;
+  IfbMapKey k = {};
+  k.ptr = ptr; k.rank = rank;
+  for (int i = 0; i < rank; ++i) { k.dims[i] = dims[i]; k.box[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) k.strides[i] = strides[i];
+  unsigned long long h = (unsigned long long)(uintptr_t)ptr * 0x9E3779B97F4A7C15ull;
+  for (int i = 0; i < rank; ++i) h = (h ^ (k.dims[i] + 0x632BE59BD9B4E019ull * k.box[i])) * 0xD6E8FEB86659FD93ull;
+  int slot = (int)((h >> 40) % SLOTS);
+  for (int probe = 0; probe < 16; ++probe, slot = (slot + 1) % SLOTS) {
+    if (used[slot] && keys[slot] == k) { *out = maps[slot]; return IFB_OK; }
+    if (!used[slot]) break;
+  }
+  if (!enc) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return IFB_ERR_ARG;
+    enc = (IfbEncodeTiledFn)fn;
+  }
+  cuuint64_t d[3] = {1, 1, 1}, st[2] = {0, 0};
+  cuuint32_t b[3] = {1, 1, 1}, es[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) st[i] = strides[i];
+  CUtensorMap m;
+  if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return IFB_ERR_ARG;
+  if (!used[slot]) { keys[slot] = k; maps[slot] = m; used[slot] = true; }      // a full neighbourhood: encode every time
+  *out = m;
+  return IFB_OK;
+}
+#endif
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -19,8 +19,8 @@
 //
 // Every wait on a barrier is bounded: after G_SPIN_LIMIT polls the thread writes a code to `*err`, raises
 // the CTA's abort flag, and everything falls through to the common exit, which frees the tensor memory.
-#include "common.cuh"
 #include <cuda.h>
+#include "common.cuh"
 
 typedef __nv_bfloat16 bf16;
 constexpr int G_BM = 128;          // tokens per tile  (MMA M)
@@ -231,33 +231,12 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 }
 
 // ---------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
 // A [rows, k] bfloat16 row-major matrix as a tensor map with boxes of 64 k x box_rows rows, 128-byte swizzle.
 static int make_map(CUtensorMap* m, const void* ptr, int rows, int k, int box_rows) {
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) return IFB_ERR_ARG;
-  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  cuuint32_t box[2] = {(cuuint32_t)G_BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? IFB_OK : IFB_ERR_ARG;
+  const unsigned long long dims[2] = {(unsigned long long)k, (unsigned long long)rows};
+  const unsigned long long strides[1] = {(unsigned long long)k * 2};
+  const unsigned box[2] = {(unsigned)G_BK, (unsigned)box_rows};
+  return ifb_tensor_map_bf16(m, ptr, 2, dims, strides, box);
 }
 
 template <int EPI, typename TO>

@@ -159,6 +159,8 @@ class ModelRunner:
         # decode-only steps are replayed from CUDA graphs, one per (batch bucket, context bucket)
         self.use_graphs = self._pin and bool(getattr(model, "graph_safe", False))
         self._graphs: Dict[tuple, tuple] = {}
+        self._shapes_seen: Dict[tuple, int] = {}
+        self.max_graphs = 64
         self.graph_replays = 0
         self.launches_per_graph_step = 0
 
@@ -212,8 +214,7 @@ class ModelRunner:
         cannot all be had."""
         self.validate(entries)
         self._reserve(entries)
-        ctx = self._build_context(entries)
-        logits = self.model.forward(ctx)
+        logits = self._execute(entries, None, None, None, sample=False)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
@@ -223,9 +224,7 @@ class ModelRunner:
                         uniforms: Sequence[float], feed=None) -> Optional[SampledTokens]:
         """``step`` followed by the sampling kernel on the wanted rows: returns the sampled token
         ids as a :class:`SampledTokens` (None if nothing is wanted); nothing here waits for the
-        device.  ``temperatures`` and ``uniforms`` have one entry per wanted row.  A step in which
-        every request brings one token and wants its logits (plain decoding) is replayed from a
-        CUDA graph.
+        device.  ``temperatures`` and ``uniforms`` have one entry per wanted row.
 
         ``feed`` = (previous step's SampledTokens, rows): the step's input tokens are not known
         to the host yet; entry i takes row ``rows[i]`` of what the previous step sampled, on the
@@ -237,14 +236,7 @@ class ModelRunner:
         if len(temperatures) != wanted or len(uniforms) != wanted:
             raise BatchError("one temperature and one uniform number per wanted row")
         self._reserve(entries)
-        decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
-        greedy = all(t == 0.0 for t in temperatures)
-        if self.use_graphs and decode_only:
-            self._graph_step(entries, temperatures, uniforms, greedy, feed)
-        else:
-            ctx = self._build_context(entries, temperatures=temperatures, uniforms=uniforms)
-            self._apply_feed(ctx, feed)
-            self._forward_and_sample(ctx, greedy)
+        self._execute(entries, temperatures, uniforms, feed, sample=True)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
@@ -273,9 +265,9 @@ class ModelRunner:
             idx = torch.tensor(list(rows), dtype=torch.int64, device=prev.device.device)
             ctx.token_ids[:n].copy_(prev.device.index_select(0, idx))
 
-    def _forward_and_sample(self, ctx, greedy: bool):
+    def _forward(self, ctx, sample: bool, greedy: bool):
         logits = self.model.forward(ctx)
-        if logits is not None:
+        if sample and logits is not None:
             m = logits.shape[0]
             if greedy:
                 self.rt.kernels.sample(logits, None, None, self.sampled[:m])
@@ -283,38 +275,65 @@ class ModelRunner:
                 self.rt.kernels.sample(logits, ctx.temperatures[:m], ctx.uniforms[:m], self.sampled[:m])
         return logits
 
-    def _graph_step(self, entries, temperatures, uniforms, greedy, feed=None) -> None:
-        r = len(entries)
-        r_bucket = 1
-        while r_bucket < r:
-            r_bucket *= 2
-        r_bucket = min(r_bucket, self.max_requests)
-        longest = max(self.cache.num_computed(e.request_id) + 1 for e in entries)
+    def _execute(self, entries, temperatures, uniforms, feed, sample: bool):
+        """The step's kernels: launched one by one, or replayed from a CUDA graph.
+
+        What a graph fixes is what the launches take from the host: the numbers of tokens, requests
+        and wanted rows, the longest portion, a bucket of the longest context (it decides how
+        attention is split) and the kind of sampling; token ids, positions, lengths, tables and
+        wanted rows are read from device buffers that keep their address.  Plain decoding (one
+        token per request) is padded to a power-of-two batch and recorded at its first
+        occurrence; any other shape is recorded when it occurs a second time (a prompt cut into
+        portions of one size, a benchmark's repeated prompt), so that one-off shapes cost no
+        recording.  A graph is dropped when a buffer it points at has moved."""
+        greedy = sample and all(t == 0.0 for t in temperatures)
+        build = dict(temperatures=temperatures, uniforms=uniforms) if sample else {}
+        if not self.use_graphs:
+            ctx = self._build_context(entries, **build)
+            self._apply_feed(ctx, feed)
+            return self._forward(ctx, sample, greedy)
+        longest = max(self.cache.num_computed(e.request_id) + len(e.tokens) for e in entries)
         seq_bucket = 256
         while seq_bucket < longest:
             seq_bucket *= 2
-        key = (r_bucket, seq_bucket, greedy)
-        ctx = self._build_context(entries, temperatures=temperatures, uniforms=uniforms, pad_to=r_bucket,
-                                  seq_bucket=seq_bucket)
+        decode_only = sample and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        if decode_only:
+            r_bucket = 1
+            while r_bucket < len(entries):
+                r_bucket *= 2
+            r_bucket = min(r_bucket, self.max_requests)
+            key = ("decode", r_bucket, seq_bucket, greedy)
+            ctx = self._build_context(entries, pad_to=r_bucket, seq_bucket=seq_bucket, **build)
+        else:
+            ctx = self._build_context(entries, seq_bucket=seq_bucket, **build)
+            key = ("any", ctx.num_tokens, ctx.num_requests, ctx.num_logit_rows, ctx.max_q_len, seq_bucket, sample, greedy)
         self._apply_feed(ctx, feed)
         stamp = (self.arena.generation, getattr(self.rt.kernels, "scratch_generation", 0))
         held = self._graphs.get(key)
         if held is not None and held[1] == stamp:
             held[0].replay()
             self.graph_replays += 1
-            return
-        # first time (or buffers moved since): run once as it is, which also makes every allocation,
-        # then record the same launches for the next time
-        self._forward_and_sample(ctx, greedy)
+            return held[2]
+        if len(self._shapes_seen) > 4096:
+            self._shapes_seen.clear()
+        seen = self._shapes_seen.get(key, 0) + 1
+        self._shapes_seen[key] = seen
+        # run once as it is (which also makes every allocation) ...
+        logits = self._forward(ctx, sample, greedy)
+        if not decode_only and seen < 2:
+            return logits
+        # ... then record the same launches for the next time; the recording runs nothing
+        if len(self._graphs) >= self.max_graphs:
+            self._graphs.pop(next(iter(self._graphs)))
         torch.cuda.synchronize()
         stamp = (self.arena.generation, getattr(self.rt.kernels, "scratch_generation", 0))
         graph = torch.cuda.CUDAGraph()
         before = getattr(self.rt.kernels, "launches", 0)
         with torch.cuda.graph(graph):
-            self._forward_and_sample(ctx, greedy)
+            recorded = self._forward(ctx, sample, greedy)
         self.launches_per_graph_step = getattr(self.rt.kernels, "launches", 0) - before
-        # the recording ran nothing; this step's result is the eager run's
-        self._graphs[key] = (graph, stamp)
+        self._graphs[key] = (graph, stamp, recorded)
+        return logits
 
     def _table_row(self, rid, gi):
         """The block table of (request, group) as an int32 array, extended by the pages taken since last
