@@ -84,6 +84,7 @@ class CudaKernels:
         self.attention_tma = True      # keys and values by TMA where the sizes allow (else 16-byte async copies)
         self.attention_tc = True       # prompts on tcgen05 where the sizes allow (head size 128, pages of 16/32/64)
         self._attn_tc = None
+        self.tc_attention_calls = 0
         self._err_armed = False
         self.tc_min_rows = 65
         self._attn_mma = {}        # head size -> library
@@ -276,6 +277,7 @@ class CudaKernels:
             self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
         self._err_armed = True
         self.launches += 1
+        self.tc_attention_calls += 1
         _check(self._attn_tc.ifb_attention_tc(
             qkv.data_ptr(), qkv.stride(0), kv_pages.data_ptr(), kv_pages.shape[0], block_tables.data_ptr(),
             block_tables.stride(0), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), self._dev_err.data_ptr(), n, r,
@@ -325,6 +327,12 @@ class CudaKernels:
                 self._attn_counters = torch.zeros(max(r * num_kv_heads, 4096), dtype=torch.int32, device="cuda")
                 self.scratch_generation += 1
             counters = self._attn_counters
+        use_tc = (not only_small and self.attention_tc and head_dim == 128 and 128 % group == 0
+                  and kv_pages.shape[3] in (16, 32, 64) and kv_pages.data_ptr() % 128 == 0)
+        if use_tc:
+            self._attention_tc(qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out, scale,
+                               window, max_q_len, n, r)
+            only_small = True          # the tile kernel's requests are done; the small-q kernel takes the rest
         self.launches += 1 + (0 if only_small else 1)
         if self._dev_err is None:
             self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
