@@ -53,11 +53,84 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     store_from_f32(out, out_dtype, (size_t)orow * hidden + h, vbuf[h] * r * load_as_f32(w, w_dtype, h));
 }
 
+// The same with a warp per row and the row in registers, for widths 128 * IT up to 2048: one pass over global
+// memory, a shuffle reduction, no shared memory and no block barrier.
+template <int IT>
+__global__ void __launch_bounds__(128)
+rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ delta, int num_splits, size_t split_stride,
+                    const void* __restrict__ w, int w_dtype, float eps, void* __restrict__ out, int out_dtype,
+                    const int* __restrict__ rows, int num_out_rows) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  constexpr int H = 128 * IT;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int orow = blockIdx.x * 4 + warp;
+  if (orow >= num_out_rows) return;
+  const int row = rows ? rows[orow] : orow;
+  float* xr = x + (size_t)row * H;
+  float4 v[IT];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int idx = (it * 32 + lane) * 4;
+    float4 a = *reinterpret_cast<const float4*>(xr + idx);
+    for (int sp = 0; sp < num_splits; ++sp) {
+      const float4 d = *reinterpret_cast<const float4*>(delta + (size_t)sp * split_stride + (size_t)row * H + idx);
+      a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+    }
+    if (!rows && num_splits) *reinterpret_cast<float4*>(xr + idx) = a;
+    v[it] = a;
+    ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int idx = (it * 32 + lane) * 4;
+    float g0, g1, g2, g3;
+    if (w_dtype == IFB_F32) {
+      const float4 g = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + idx);
+      g0 = g.x; g1 = g.y; g2 = g.z; g3 = g.w;
+    } else {
+      const uint2 g = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(w) + idx);
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&g.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&g.y);
+      g0 = __low2float(lo); g1 = __high2float(lo); g2 = __low2float(hi); g3 = __high2float(hi);
+    }
+    const float y0 = v[it].x * r * g0, y1 = v[it].y * r * g1, y2 = v[it].z * r * g2, y3 = v[it].w * r * g3;
+    if (out_dtype == IFB_F32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)orow * H + idx) = make_float4(y0, y1, y2, y3);
+    } else {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+      uint2 pk;
+      pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)orow * H + idx) = pk;
+    }
+  }
+}
+
+template <int IT>
+static int rmsnorm_warp_launch(float* x, const float* delta, int num_splits, size_t split_stride, const void* w, int w_dtype,
+                               float eps, void* out, int out_dtype, const int* rows, int num_out_rows, cudaStream_t stream) {
+  return ifb_launch(rmsnorm_warp_kernel<IT>, dim3((num_out_rows + 3) / 4), dim3(128), 0, stream, x, delta, num_splits, split_stride, w,
+                    w_dtype, eps, out, out_dtype, rows, num_out_rows);
+}
+
 IFB_EXPORT int ifb_rmsnorm(float* x, const float* delta, int num_splits, long long split_stride, const void* w,
                            int w_dtype, float eps, void* out, int out_dtype, const int* rows, int num_out_rows,
                            int hidden, cudaStream_t stream) {
   if (num_out_rows <= 0) return IFB_OK;
   if ((w_dtype != IFB_F32 && w_dtype != IFB_BF16) || (out_dtype != IFB_F32 && out_dtype != IFB_BF16)) return IFB_ERR_DTYPE;
+  // many rows: a warp per row; few rows (decoding): a block per row is the shorter chain
+  if (num_out_rows >= 64 && hidden % 128 == 0 && hidden <= 2048 && !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) &&
+      (split_stride % 4) == 0) {
+    const int ns = delta ? num_splits : 0;
+#define IFB_RMS_CASE(IT) case IT: return rmsnorm_warp_launch<IT>(x, delta, ns, (size_t)split_stride, w, w_dtype, eps, out, out_dtype, rows, num_out_rows, stream);
+    switch (hidden / 128) {
+      IFB_RMS_CASE(1) IFB_RMS_CASE(2) IFB_RMS_CASE(3) IFB_RMS_CASE(4) IFB_RMS_CASE(5) IFB_RMS_CASE(6) IFB_RMS_CASE(7) IFB_RMS_CASE(8)
+      IFB_RMS_CASE(9) IFB_RMS_CASE(10) IFB_RMS_CASE(11) IFB_RMS_CASE(12) IFB_RMS_CASE(13) IFB_RMS_CASE(14) IFB_RMS_CASE(15) IFB_RMS_CASE(16)
+    }
+#undef IFB_RMS_CASE
+  }
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return IFB_ERR_SIZE;
   static size_t configured = 0;
@@ -72,6 +145,29 @@ IFB_EXPORT int ifb_rmsnorm(float* x, const float* delta, int num_splits, long lo
 }
 
 // ------------------------------------------------------------------------------------------
+// rope_table: table[tok][i] = (cos, sin)(positions[tok] * inv_freq[i]), i < half.  A step computes it once and
+// every layer's rotation reads it (the angles do not depend on the layer).
+// ------------------------------------------------------------------------------------------
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int half,
+                                  float2* __restrict__ table, int n_tokens) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_tokens * half) return;
+  float s, c;
+  sincosf((float)positions[idx / half] * inv_freq[idx % half], &s, &c);
+  table[idx] = make_float2(c, s);
+}
+
+IFB_EXPORT int ifb_rope_table(const int* positions, const float* inv_freq, int half, float* table, int n_tokens,
+                              cudaStream_t stream) {
+  if (n_tokens <= 0 || half <= 0) return IFB_OK;
+  const long long total = (long long)n_tokens * half;
+  return ifb_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, positions, inv_freq, half,
+                    reinterpret_cast<float2*>(table), n_tokens);
+}
+
+// ------------------------------------------------------------------------------------------
 // qk_norm_rope_store: one warp per (token, head) of the fused qkv row [q heads | k heads | v heads].
 //   q, k heads: optional RMSNorm over the head (weight shared by all heads), optional rotation of
 //   the first rotary_dim elements by angle position * inv_freq[i]; written back in place.
@@ -81,7 +177,8 @@ IFB_EXPORT int ifb_rmsnorm(float* x, const float* delta, int num_splits, long lo
 template <typename T>
 __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv, int d,
                                           const void* __restrict__ qw, const void* __restrict__ kw, int w_dtype,
-                                          float eps, const float* __restrict__ inv_freq, int rotary_dim,
+                                          float eps, const float* __restrict__ inv_freq,
+                                          const float* __restrict__ rope_table, int rotary_dim,
                                           int interleaved, const int* __restrict__ positions,
                                           const int* __restrict__ slots, T* __restrict__ pages, int page_size) {
   extern __shared__ float sm[];
@@ -130,7 +227,8 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int n_tokens, int
       if (interleaved) { first = (i & 1) == 0; pair = first ? i + 1 : i - 1; fi = i >> 1; }
       else { first = i < half; pair = first ? i + half : i - half; fi = first ? i : i - half; }
       float s, c;
-      sincosf(pos * inv_freq[fi], &s, &c);
+      if (rope_table) { const float2 t = reinterpret_cast<const float2*>(rope_table)[(size_t)tok * half + fi]; c = t.x; s = t.y; }
+      else sincosf(pos * inv_freq[fi], &s, &c);
       const float o = buf[pair];
       v = first ? v * c - o * s : v * c + o * s;
     }
@@ -151,8 +249,8 @@ template <typename T, int EPL>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv, const void* __restrict__ qw,
                               const void* __restrict__ kw, int w_dtype, float eps, const float* __restrict__ inv_freq,
-                              const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ pages,
-                              int page_size) {
+                              const float* __restrict__ rope_table, const int* __restrict__ positions,
+                              const int* __restrict__ slots, T* __restrict__ pages, int page_size) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
   constexpr int d = 32 * EPL;
@@ -167,9 +265,15 @@ qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv
   // cos and sin of this lane's EPL angles, once for all heads of the block (lanes l and l ^ 16 share them)
   float cs[EPL], sn[EPL];
   if (inv_freq != nullptr && head0 < nq + nkv) {
-    const float pos = (float)positions[tok];
+    if (rope_table) {
+      const float2* t = reinterpret_cast<const float2*>(rope_table) + (size_t)tok * (d / 2) + (lane & 15) * EPL;
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) sincosf(pos * inv_freq[(lane & 15) * EPL + e], &sn[e], &cs[e]);
+      for (int e = 0; e < EPL; ++e) { cs[e] = t[e].x; sn[e] = t[e].y; }
+    } else {
+      const float pos = (float)positions[tok];
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) sincosf(pos * inv_freq[(lane & 15) * EPL + e], &sn[e], &cs[e]);
+    }
   }
   for (int head = head0; head < min(heads, head0 + QK_HPW); ++head) {
     T* src = qkv + (size_t)tok * heads * d + (size_t)head * d + lane * EPL;
@@ -215,22 +319,22 @@ qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv
 
 template <typename T>
 static int qk_vec_launch(int epl, unsigned blocks, cudaStream_t stream, T* qkv, int n_tokens, int nq, int nkv, const void* qw,
-                         const void* kw, int w_dtype, float eps, const float* inv_freq, const int* positions, const int* slots,
-                         T* pages, int page_size) {
+                         const void* kw, int w_dtype, float eps, const float* inv_freq, const float* rope_table,
+                         const int* positions, const int* slots, T* pages, int page_size) {
   if (epl == 2)
     return ifb_launch(qk_norm_rope_store_vec_kernel<T, 2>, dim3(blocks), dim3(128), 0, stream, qkv, n_tokens, nq, nkv, qw, kw,
-                      w_dtype, eps, inv_freq, positions, slots, pages, page_size);
+                      w_dtype, eps, inv_freq, rope_table, positions, slots, pages, page_size);
   if (epl == 4)
     return ifb_launch(qk_norm_rope_store_vec_kernel<T, 4>, dim3(blocks), dim3(128), 0, stream, qkv, n_tokens, nq, nkv, qw, kw,
-                      w_dtype, eps, inv_freq, positions, slots, pages, page_size);
+                      w_dtype, eps, inv_freq, rope_table, positions, slots, pages, page_size);
   return ifb_launch(qk_norm_rope_store_vec_kernel<T, 8>, dim3(blocks), dim3(128), 0, stream, qkv, n_tokens, nq, nkv, qw, kw,
-                    w_dtype, eps, inv_freq, positions, slots, pages, page_size);
+                    w_dtype, eps, inv_freq, rope_table, positions, slots, pages, page_size);
 }
 
 IFB_EXPORT int ifb_qk_norm_rope_store(void* qkv, int dtype, int n_tokens, int nq, int nkv, int d, const void* qw,
-                                      const void* kw, int w_dtype, float eps, const float* inv_freq, int rotary_dim,
-                                      int interleaved, const int* positions, const int* slots, void* pages,
-                                      int page_size, cudaStream_t stream) {
+                                      const void* kw, int w_dtype, float eps, const float* inv_freq,
+                                      const float* rope_table, int rotary_dim, int interleaved, const int* positions,
+                                      const int* slots, void* pages, int page_size, cudaStream_t stream) {
   if (n_tokens <= 0) return IFB_OK;
   if (d < 1 || d > 1024) return IFB_ERR_SIZE;
   if (inv_freq && (rotary_dim < 2 || rotary_dim > d || (rotary_dim & 1) || !positions)) return IFB_ERR_ARG;
@@ -245,18 +349,18 @@ IFB_EXPORT int ifb_qk_norm_rope_store(void* qkv, int dtype, int n_tokens, int nq
     const unsigned vblocks = (unsigned)((vitems + warps - 1) / warps);
     if (dtype == IFB_F32)
       return qk_vec_launch<float>(d / 32, vblocks, stream, (float*)qkv, n_tokens, nq, nkv, qw, kw, w_dtype, eps, inv_freq,
-                                  positions, slots, (float*)pages, page_size);
+                                  rope_table, positions, slots, (float*)pages, page_size);
     return qk_vec_launch<__nv_bfloat16>(d / 32, vblocks, stream, (__nv_bfloat16*)qkv, n_tokens, nq, nkv, qw, kw, w_dtype, eps,
-                                        inv_freq, positions, slots, (__nv_bfloat16*)pages, page_size);
+                                        inv_freq, rope_table, positions, slots, (__nv_bfloat16*)pages, page_size);
   }
   const size_t smem = (size_t)warps * d * sizeof(float);
   if (dtype == IFB_F32)
     return ifb_launch(qk_norm_rope_store_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream, (float*)qkv, n_tokens,
-                      nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rotary_dim, interleaved, positions, slots, (float*)pages,
+                      nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rope_table, rotary_dim, interleaved, positions, slots, (float*)pages,
                       page_size);
   if (dtype == IFB_BF16)
     return ifb_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream,
-                      (__nv_bfloat16*)qkv, n_tokens, nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rotary_dim, interleaved,
+                      (__nv_bfloat16*)qkv, n_tokens, nq, nkv, d, qw, kw, w_dtype, eps, inv_freq, rope_table, rotary_dim, interleaved,
                       positions, slots, (__nv_bfloat16*)pages, page_size);
   return IFB_ERR_DTYPE;
 }

@@ -98,6 +98,7 @@ class StepContext:
         self.max_seq_len = 0
         self.token_ids = self.positions = self.cu_q = self.seq_lens = None
         self.state_slots = self.first_portion = self.logit_rows = self.req_index = None
+        self.shared: Dict[tuple, torch.Tensor] = {}       # what parts compute once per step and share (keyed by the part)
         self.group_slot_mapping: List[torch.Tensor] = []
         self.group_block_tables: List[torch.Tensor] = []
         # host copies, for parts written with torch operations
@@ -329,6 +330,7 @@ class ModelRunner:
         stamp = (self.arena.generation, getattr(self.rt.kernels, "scratch_generation", 0))
         graph = torch.cuda.CUDAGraph()
         before = getattr(self.rt.kernels, "launches", 0)
+        ctx.shared.clear()             # what parts computed once for the step is computed in the recording too
         with torch.cuda.graph(graph):
             recorded = self._forward(ctx, sample, greedy)
         self.launches_per_graph_step = getattr(self.rt.kernels, "launches", 0) - before

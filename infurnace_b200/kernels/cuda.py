@@ -65,8 +65,9 @@ class CudaKernels:
         c.ifb_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_void_p, c_int,
                                   c_void_p, c_int, c_int, c_void_p]
         c.ifb_qk_norm_rope_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
-                                             c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                              c_void_p]
+        c.ifb_rope_table.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]
         c.ifb_sample.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
         c.ifb_linear_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_void_p]
@@ -209,8 +210,19 @@ class CudaKernels:
                                            _ptr(counters), n, o, k, epi, splits, self._stream()), "linear")
 
     # ------------------------------------------------------------------ q/k norm, rotation, store
+    def rope_table(self, positions, inv_freq, out):
+        """out[tok, i] = (cos, sin)(positions[tok] * inv_freq[i]), float32 ``[tokens, 2 * len(inv_freq)]``."""
+        _dense(positions, "positions", torch.int32), _dense(inv_freq, "inv_freq", torch.float32)
+        _dense(out, "out", torch.float32)
+        n, half = positions.numel(), inv_freq.numel()
+        if out.shape != (n, 2 * half):
+            raise KernelError("rope_table: out is [tokens, 2 * len(inv_freq)]")
+        self.launches += 1
+        _check(self.core.ifb_rope_table(positions.data_ptr(), inv_freq.data_ptr(), half, out.data_ptr(), n, self._stream()),
+               "rope_table")
+
     def qk_norm_rope_store(self, qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, inv_freq,
-                           rotary_dim, interleaved, positions, slot_mapping, kv_pages):
+                           rotary_dim, interleaved, positions, slot_mapping, kv_pages, rope_table=None):
         _dense(qkv, "qkv")
         n = qkv.shape[0]
         if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
@@ -228,6 +240,10 @@ class CudaKernels:
             _dense(inv_freq, "inv_freq", torch.float32), _dense(positions, "positions", torch.int32)
             if inv_freq.numel() != rotary_dim // 2 or positions.numel() != n:
                 raise KernelError("qk_norm_rope_store: inv_freq or positions has the wrong length")
+            if rope_table is not None:
+                _dense(rope_table, "rope_table", torch.float32)
+                if rope_table.shape != (n, rotary_dim):
+                    raise KernelError("qk_norm_rope_store: rope_table is [tokens, rotary_dim]")
         page_size = 1
         if slot_mapping is not None:
             _dense(slot_mapping, "slot_mapping", torch.int32), _dense(kv_pages, "kv_pages", qkv.dtype)
@@ -238,7 +254,8 @@ class CudaKernels:
         self.launches += 1
         _check(self.core.ifb_qk_norm_rope_store(
             qkv.data_ptr(), _code(qkv), n, num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight), wd,
-            float(eps), _ptr(inv_freq), int(rotary_dim), int(bool(interleaved)), _ptr(positions), _ptr(slot_mapping),
+            float(eps), _ptr(inv_freq), _ptr(rope_table) if inv_freq is not None else 0, int(rotary_dim),
+            int(bool(interleaved)), _ptr(positions), _ptr(slot_mapping),
             _ptr(kv_pages) if slot_mapping is not None else 0, page_size, self._stream()), "qk_norm_rope_store")
 
     # ------------------------------------------------------------------ attention

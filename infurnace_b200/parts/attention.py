@@ -46,8 +46,9 @@ class PagedAttention:
         fused = self.position.fused_rotary() if self.position is not None else None
         if self.position is None or fused is not None:
             inv_freq, rdim, inter = fused if fused is not None else (None, 0, False)
+            table = self.position.table(ctx) if fused is not None and hasattr(self.position, "table") else None
             k.qk_norm_rope_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm_w, self.k_norm_w,
-                                 self.eps, inv_freq, rdim, inter, ctx.positions, slots, kv.pages)
+                                 self.eps, inv_freq, rdim, inter, ctx.positions, slots, kv.pages, rope_table=table)
         else:   # a position code without a fused form: norm, then the code, then the store
             k.qk_norm_rope_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm_w, self.k_norm_w,
                                  self.eps, None, 0, False, ctx.positions, None, None)

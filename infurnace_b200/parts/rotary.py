@@ -27,6 +27,18 @@ class Rotary:
     def fused_rotary(self):
         return self.inv_freq, self.spec.rotary_dim, self.spec.interleaved
 
+    def table(self, ctx):
+        """(cos, sin) of every token's angles, computed once per step and shared by all layers with the same
+        base and rotated width (the angles do not depend on the layer)."""
+        key = ("rope_table", self.spec.theta, self.spec.rotary_dim)
+        t = ctx.shared.get(key)
+        if t is None:
+            t = ctx.buffer(f"rope_table_{self.spec.theta}_{self.spec.rotary_dim}", (ctx.num_tokens, self.spec.rotary_dim),
+                           torch.float32)
+            self.k.rope_table(ctx.positions, self.inv_freq, t)
+            ctx.shared[key] = t
+        return t
+
     def apply(self, qkv, num_heads, num_kv_heads, head_dim, positions):
         self.k.qk_norm_rope_store(qkv, num_heads, num_kv_heads, head_dim, None, None, 0.0,
                                   self.inv_freq, self.spec.rotary_dim, self.spec.interleaved,

@@ -62,8 +62,13 @@ class ReferenceKernels:
         out.copy_(y.to(out.dtype))
 
     # ------------------------------------------------------------------ q/k norm, rotation, store
+    def rope_table(self, positions, inv_freq, out):
+        """out[tok] = (cos, sin) pairs of positions[tok] * inv_freq[i], interleaved: [tokens, 2 * len(inv_freq)]."""
+        ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
+        out.copy_(torch.stack((ang.cos(), ang.sin()), dim=-1).flatten(-2))
+
     def qk_norm_rope_store(self, qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps,
-                           inv_freq, rotary_dim, interleaved, positions, slot_mapping, kv_pages):
+                           inv_freq, rotary_dim, interleaved, positions, slot_mapping, kv_pages, rope_table=None):
         """In place on qkv [N, (nq + 2 nkv) d]: per-head RMSNorm of the q and k heads (when
         the weights are given), rotation of q and k by the token's position (when inv_freq
         is given), then k and v are written to the pages at ``slot_mapping`` (slot =
@@ -82,8 +87,12 @@ class ReferenceKernels:
         if k_weight is not None:
             k = norm(k, k_weight)
         if inv_freq is not None:
-            ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
-            cos, sin = ang.cos().to(self.cd)[:, None, :], ang.sin().to(self.cd)[:, None, :]
+            if rope_table is not None:
+                pairs = rope_table.view(N, rotary_dim // 2, 2)
+                cos, sin = pairs[..., 0].to(self.cd)[:, None, :], pairs[..., 1].to(self.cd)[:, None, :]
+            else:
+                ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
+                cos, sin = ang.cos().to(self.cd)[:, None, :], ang.sin().to(self.cd)[:, None, :]
 
             def rot(t):
                 r, rest = t[..., :rotary_dim], t[..., rotary_dim:]
