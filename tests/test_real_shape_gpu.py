@@ -15,15 +15,25 @@ import tiny
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def model(tmp_path_factory):
+# the layer sizes of the three checkpoints the benchmarks name; the two large ones with one layer and a small
+# vocabulary, so that the plain implementation on the CPU stays within seconds
+SHAPES = {
+    "0.6b": ("qwen3-0.6b.json", dict(num_hidden_layers=2)),
+    "8b": ("qwen3-8b.json", dict(num_hidden_layers=1, vocab_size=4096)),          # 32 / 8 heads, hidden 4096, mlp 12288
+    "32b": ("qwen3-32b.json", dict(num_hidden_layers=1, vocab_size=4096)),        # 64 / 8 heads, hidden 5120, mlp 25600
+}
+
+
+@pytest.fixture(scope="module", params=list(SHAPES))
+def model(request, tmp_path_factory):
     from infurnace_b200.models import config_from_dict
     from infurnace_b200.weights.random_init import write_random_model
     from safetensors.torch import load_file, save_file
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    with open(os.path.join(root, "configs", "qwen3-0.6b.json")) as f:
+    file_name, changes = SHAPES[request.param]
+    with open(os.path.join(root, "configs", file_name)) as f:
         d = json.load(f)
-    d["num_hidden_layers"] = 2
+    d.update(changes)
     cfg = config_from_dict(d)
     path = str(tmp_path_factory.mktemp("real") / "m")
     write_random_model(cfg, 3, path)
@@ -38,7 +48,7 @@ def model(tmp_path_factory):
     return path, cfgd, toks, P.forward(cfgd, w, toks)
 
 
-@pytest.mark.parametrize("dtype,tolerance", [("float32", 1e-4), ("bfloat16", 0.12)])
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 2e-5), ("bfloat16", 0.05)])   # times the size of the largest logit
 def test_real_layer_sizes(model, dtype, tolerance):
     from infurnace_b200.engine.loading import EngineOptions, build_runner
     path, cfg, toks, ref = model
