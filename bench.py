@@ -205,7 +205,7 @@ def run_ours(args):
     cfg = read_config(os.path.join(ROOT, "configs", "qwen3-0.6b.json"))
     batch, steps, warmup = args.batch, args.steps, args.warmup
     layers_full = cfg.num_hidden_layers
-    page = 16
+    page = args.page_size
     big = 64 if args.mode == "all" else batch          # the largest batch of the run
     pool_tokens = big * CONTEXT + PREFILL_TOKENS + 64
     with tempfile.TemporaryDirectory(prefix="infurnace_b200_bench_") as d:
@@ -350,6 +350,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--page-size", type=int, default=16, help="tokens per page of the key/value cache")
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--mode", default="all", choices=("all", "decode", "prefill"),
                     help="decode / prefill: only that part, on a pool just large enough (for profiling a small case)")

@@ -34,16 +34,25 @@
 typedef __nv_bfloat16 bf16;
 constexpr int D = 128;
 constexpr int ROWS = 128;                 // score rows per CTA (MMA M)
-constexpr int BK = 128;                   // keys per tile (MMA N of S, K of PV)
-constexpr int TC_THREADS = 192;
+constexpr int BK = 128;                   // keys per tile loaded
+constexpr int SUB = 64;                   // keys per score buffer (MMA N of S, K of P V per half)
+constexpr int TC_THREADS = 384;                // producer warp, two MMA warps, an idle warp, two softmax groups of four
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 constexpr int HALF_BYTES = 128 * 128;     // a [128 rows][64 columns] bf16 half tile in the 128-byte swizzle: 16 KB
 constexpr int TILE_BYTES = 2 * HALF_BYTES;
-constexpr int SMEM_BYTES = 3 * TILE_BYTES /* Q, K, V */ + 1024 /* alignment */;       // 97 KB: two CTAs per SM
-// tensor memory columns (32-bit): S [0,128) with P (bfloat16 pairs) written over its first 64 as the row is
-// consumed, O [128,256).  256 columns per CTA: two CTAs share an SM's 512.
-constexpr int COL_S = 0, COL_P = 0, COL_O = 128, TMEM_COLS = 256;
+constexpr int SMEM_BYTES = 6 * TILE_BYTES /* 2 Q, 2 K, 2 V */ + 1024 /* alignment */;   // 193 KB: one CTA per SM
+// tensor memory columns (32-bit), per query tile: S [0,128) with P (bfloat16 pairs) written over its first 64 once
+// the row has been read, O [128,256).  Two query tiles: all 512 columns of the SM.
+constexpr int COL_S = 0, COL_O = 128, COLS_PER_TILE = 256, TMEM_COLS = 512;
 constexpr int NO_ROW = -1000000000;
+
+#ifdef TC_TRACE
+// Timestamps of the phases of one CTA (the one with the longest key range of head 0), for tuning builds only.
+__device__ long long tc_trace_buf[4][64][8];
+#define TC_STAMP(who, j, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64) tc_trace_buf[who][j][k] = clock64(); } while (0)
+#else
+#define TC_STAMP(who, j, k) do {} while (0)
+#endif
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void tc_mbar_init(uint64_t* bar, int count) {
@@ -77,6 +86,13 @@ __device__ __forceinline__ void tc_tma_2d(void* smem, const CUtensorMap* map, ui
 __device__ __forceinline__ void tc_tma_3d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
                ::"r"(tc_smem_u32(smem)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// True in exactly one lane of a converged warp.  Code under it is known to the compiler as single-threaded, which lets
+// it keep the descriptors of the copies and products it issues in uniform registers.
+__device__ __forceinline__ bool tc_elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -113,6 +129,13 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
         "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
@@ -142,47 +165,70 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
   return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)(HALF_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
          (2ull << 61);
 }
-// float32 accumulator, bfloat16 A and B, M = 128, N = 128; B K-major for S = Q K^T, MN-major for O += P V.
-constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-constexpr uint32_t IDESC_PV = IDESC_S | (1u << 16);
+// float32 accumulator, bfloat16 A and B, M = 128; S = Q K^T: N = 64 keys, B K-major; O += P V: N = 128 (the head
+// size), B MN-major.
+constexpr uint32_t IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 4) << 24);
+constexpr uint32_t IDESC_S = IDESC_BASE | ((uint32_t)(SUB >> 3) << 17);
+constexpr uint32_t IDESC_PV = IDESC_BASE | ((uint32_t)(128 >> 3) << 17) | (1u << 16);
 
-__global__ void __launch_bounds__(TC_THREADS, 2)
+// One softmax group: four warps, one thread per score row of query tile `x`.
+struct TcBars {
+  uint64_t q_full, k_full[2], v_full[2], k_empty[2][2], v_empty[2][2], s_full[2][2], p_ready[2][2], o_done[2];   // [query tile][stage or buffer]
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
 attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, int total_rows,
                     int* __restrict__ err, const int* __restrict__ block_tables, int bt_stride,
                     const int* __restrict__ cu_q, const int* __restrict__ seq_lens, bf16* __restrict__ out, int nq, int nkv,
                     int page_size, float scale_log2, int window) {
   extern __shared__ unsigned char tc_smem_raw[];
-  __shared__ uint64_t q_full, k_full, v_full, k_empty, v_empty, s_full, p_ready, o_done;
+  __shared__ TcBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
   const uint32_t raw = tc_smem_u32(tc_smem_raw);
   unsigned char* smem = tc_smem_raw + (((raw + 1023u) & ~1023u) - raw);
-  unsigned char* Qs = smem;                                  // [2 halves][128 rows][128 bytes]
-  unsigned char* Ks = smem + TILE_BYTES;                     // K tile, same layout
-  unsigned char* Vs = smem + 2 * TILE_BYTES;                 // V tile
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned char* Qs = smem;                                  // two query tiles, each [2 halves][128 rows][128 bytes]
+  unsigned char* Ks = smem + 2 * TILE_BYTES;                 // two stages of K tiles, same layout
+  unsigned char* Vs = smem + 4 * TILE_BYTES;                 // two stages of V tiles
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;     // warp-uniform
   const int kvh = blockIdx.y, r = blockIdx.z;
   const int G = nq / nkv;
   const int q0 = cu_q[r], q_len = cu_q[r + 1] - q0, L = seq_lens[r];
   if (q_len * G <= 16) return;                               // the small-q kernel's request
-  const int tpc = ROWS / G;                                  // tokens per CTA
-  const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * tpc;    // longest key ranges first
+  const int tpt = ROWS / G;                                  // tokens per query tile; a CTA takes two tiles
+  const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * 2 * tpt;   // longest key ranges first
   if (t0 >= q_len) return;
-  const int t1 = min(q_len, t0 + tpc);
+  const int t1 = min(q_len, t0 + 2 * tpt);
   const int p_first = L - q_len;
   const int lo = window > 0 ? max(0, p_first + t0 - window + 1) : 0, hi = p_first + t1 - 1;
   const int T0 = (lo / BK) * BK;
-  const int n_tiles = hi >= lo ? (hi + 1 - T0 + BK - 1) / BK : 0;
+  // Keys are loaded in tiles of 128 and worked on in halves of 64: n_x[x] halves for query tile x (the second tile's
+  // tokens come later, it sees at least as far).
+  int n_x[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int t0x = t0 + x * tpt;
+    const int hix = p_first + min(q_len, t0x + tpt) - 1;
+    n_x[x] = (t0x < q_len && hix >= T0) ? (hix + 1 - T0 + SUB - 1) / SUB : 0;
+  }
+  const int n_sub = max(n_x[0], n_x[1]);
+  const int n_tiles = (n_sub + 1) / 2;
   const int* bt = block_tables + (size_t)r * bt_stride;
   const int ps_shift = __ffs(page_size) - 1;
 
   if (threadIdx.x == 0) {
-    tc_mbar_init(&q_full, 1);
-    tc_mbar_init(&k_full, 1); tc_mbar_init(&v_full, 1); tc_mbar_init(&k_empty, 1); tc_mbar_init(&v_empty, 1);
-    tc_mbar_init(&s_full, 1);
-    tc_mbar_init(&p_ready, 128);
-    tc_mbar_init(&o_done, 1);
+    tc_mbar_init(&bars.q_full, 1);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      tc_mbar_init(&bars.k_full[i], 1); tc_mbar_init(&bars.v_full[i], 1);
+      tc_mbar_init(&bars.o_done[i], 1);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        tc_mbar_init(&bars.k_empty[i][h], 1); tc_mbar_init(&bars.v_empty[i][h], 1);
+        tc_mbar_init(&bars.s_full[i][h], 1); tc_mbar_init(&bars.p_ready[i][h], 128);
+      }
+    }
     abort_word = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -199,19 +245,30 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   if (warp == 0) {
     // ---------------- producer
     if (lane == 0) {
-      tc_mbar_expect_tx(&q_full, TILE_BYTES);
-      tc_tma_3d(Qs, &q_map, &q_full, 0, kvh * G, q0 + t0);
-      tc_tma_3d(Qs + HALF_BYTES, &q_map, &q_full, 64, kvh * G, q0 + t0);
+      tc_mbar_expect_tx(&bars.q_full, (n_x[1] > 0 ? 2 : 1) * TILE_BYTES);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+        if (n_x[x] > 0 || x == 0) {
+          tc_tma_3d(Qs + x * TILE_BYTES, &q_map, &bars.q_full, 0, kvh * G, q0 + t0 + x * tpt);
+          tc_tma_3d(Qs + x * TILE_BYTES + HALF_BYTES, &q_map, &bars.q_full, 64, kvh * G, q0 + t0 + x * tpt);
+        }
     }
     const int ppt = BK >> ps_shift;                          // pages per tile: 8, 4 or 2
     const int n_ops = ppt * 2;                               // x 2 halves: at most 16 per tile
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j & 1;
 #pragma unroll
       for (int kv = 0; kv < 2; ++kv) {                       // the K tile, then the V tile
-        uint64_t* full = kv ? &v_full : &k_full;
-        if (j > 0) ok = tc_mbar_wait(kv ? &v_empty : &k_empty, (j - 1) & 1, abort_flag, err, 11);
+        uint64_t* full = kv ? &bars.v_full[st] : &bars.k_full[st];
+        if (j >= 2) {                                        // the tile two back has left this stage, for both query tiles
+#pragma unroll
+          for (int x = 0; x < 2; ++x)
+            if (ok && 2 * (j - 2) < n_x[x])
+              ok = tc_mbar_wait(kv ? &bars.v_empty[x][st] : &bars.k_empty[x][st], ((j >> 1) - 1) & 1, abort_flag, err, 11);
+        }
         if (!ok) break;
+        if (lane == 0) TC_STAMP(0, j, kv);
         if (lane == 0) tc_mbar_expect_tx(full, TILE_BYTES);
         __syncwarp();
         if (lane < n_ops) {
@@ -219,78 +276,123 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           const int key0 = T0 + j * BK + pg * page_size;
           int y = total_rows;                                // beyond the tensor: zeros
           if (key0 <= hi && key0 + page_size - 1 >= lo) y = ((bt[key0 >> ps_shift] * 2 + kv) * nkv + kvh) * page_size;
-          tc_tma_2d((kv ? Vs : Ks) + half * HALF_BYTES + pg * page_size * 128, &kv_map, full, half * 64, y);
+          tc_tma_2d((kv ? Vs : Ks) + st * TILE_BYTES + half * HALF_BYTES + pg * page_size * 128, &kv_map, full, half * 64, y);
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer
-    if (lane == 0) {
-      bool ok = tc_mbar_wait(&q_full, 0, abort_flag, err, 12);
-      const uint32_t q_addr = tc_smem_u32(Qs);
-      const uint32_t k_addr = tc_smem_u32(Ks), v_addr = tc_smem_u32(Vs);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        ok = tc_mbar_wait(&k_full, j & 1, abort_flag, err, 13);
-        if (!ok) break;
-        tc_fence_after();
-        // S = Q K^T: 8 steps of 16 along the head size, 4 per 64-column half.  (S lies where the previous tile's P
-        // lay; the tensor core takes its operations in the order they were issued, the previous P V first.)
+  } else if (warp == 1 || warp == 2) {
+    // ---------------- MMA issuers, one warp per query tile x.  The tile has two score buffers S[0], S[1] of 64 keys;
+    // half u of the keys goes to S[u & 1], and P(u) is written over its first columns.  The tensor core takes a warp's
+    // operations in the order they are issued:
+    //   S(0) S(1) | O(u) S(u+2) | ...
+    // so the scores of the next half are there before the softmax of this half ends, and S(u+2) lands where P(u)
+    // lay only after O(u) has read it.  While one warp checks its barriers the other's products keep the pipe full.
+    const int x = warp - 1;
+    const int n_mine = x ? n_x[1] : n_x[0];
+    bool ok = n_mine > 0 && tc_mbar_wait(&bars.q_full, 0, abort_flag, err, 12);
+    const uint32_t q_addr = tc_smem_u32(Qs) + x * TILE_BYTES, k_addr = tc_smem_u32(Ks), v_addr = tc_smem_u32(Vs);
+    const uint32_t tb = tmem + x * COLS_PER_TILE;
+    auto issue_qk = [&](int u) {
+      // S[u & 1] = Q K^T for 64 keys: 8 steps of 16 along the head size, 4 per 64-column half of Q and K; then the
+      // tile of keys is released if this was its last half
+      const int st = (u >> 1) & 1;
+      if (tc_elect_one()) {
+        const uint64_t qd = desc_k_major(q_addr), kd = desc_k_major(k_addr + st * TILE_BYTES + (u & 1) * (SUB * 128));
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          tc_mma_ss(tmem + COL_S, desc_k_major(q_addr + off), desc_k_major(k_addr + off), IDESC_S, ks != 0);
+          const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;       // descriptor addresses count 16 bytes
+          tc_mma_ss(tb + COL_S + (u & 1) * SUB, qd + off, kd + off, IDESC_S, ks != 0);
         }
-        tc_commit(&k_empty);
-        tc_commit(&s_full);
-        ok = tc_mbar_wait(&p_ready, j & 1, abort_flag, err, 14) && tc_mbar_wait(&v_full, j & 1, abort_flag, err, 18);
-        if (!ok) break;
-        tc_fence_after();
-        // O += P V: 8 steps of 16 keys; P at 8 columns (16 bfloat16) per step, V 2048 bytes (16 key rows) per step
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          tc_mma_ts(tmem + COL_O, tmem + COL_P + ks * 8, desc_mn_major(v_addr + ks * 2048), IDESC_PV, (j | ks) != 0);
-        tc_commit(&v_empty);
-        tc_commit(&o_done);
+        tc_commit(&bars.s_full[x][u & 1]);
+        if ((u & 1) || u == n_mine - 1) tc_commit(&bars.k_empty[x][st]);
       }
-    }
-  } else {
-    // ---------------- softmax, one thread per row
-    const int qd = warp & 3;                                 // this warp's quarter of the 128 lanes
-    const int row = qd * 32 + lane;
-    const int tok = t0 + row / G;
-    const int p = tok < t1 ? p_first + tok : NO_ROW;
-    const int row_lo = window > 0 ? p - window + 1 : 0;
-    const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
-    float m_used = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      ok = __all_sync(0xffffffffu, tc_mbar_wait(&s_full, j & 1, abort_flag, err, 15)) != 0;    // warp-uniform
+      __syncwarp();
+    };
+    auto wait_k = [&](int u) {                               // half u opens a new tile of keys
+      if (!(u & 1)) {
+        ok = ok && tc_mbar_wait(&bars.k_full[(u >> 1) & 1], (u >> 2) & 1, abort_flag, err, 13);
+        tc_fence_after();
+      }
+    };
+    if (ok) { wait_k(0); if (ok) issue_qk(0); }
+    if (ok && n_mine > 1) issue_qk(1);
+    for (int u = 0; u < n_mine && ok; ++u) {
+      const int st = (u >> 1) & 1;
+      if (x == 0) TC_STAMP(1, u, 0);
+      if (!(u & 1)) ok = tc_mbar_wait(&bars.v_full[st], (u >> 2) & 1, abort_flag, err, 18);
+      ok = ok && tc_mbar_wait(&bars.p_ready[x][u & 1], (u >> 1) & 1, abort_flag, err, 14);
       if (!ok) break;
       tc_fence_after();
-      const int key0 = T0 + j * BK;
-      // a tile every key of which every row of the CTA sees needs no masking (rows past the request's tokens are
-      // computed like the others and never stored)
-      const bool interior = key0 >= lo && key0 + BK - 1 <= min(hi, p_first + t0) && (window == 0 || key0 >= hi - window + 1);
-      // pass 1: the row's maximum over the visible keys of the tile
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tc_ld32(lane_addr + COL_S + c * 32, v);
-        tc_wait_ld();
-        if (interior) {
+      if (x == 0) TC_STAMP(1, u, 1);
+      // O += P(u) V: 4 steps of 16 keys; P at 8 columns (16 bfloat16) per step, V 2048 bytes (16 key rows) per step
+      if (tc_elect_one()) {
+        const uint64_t vd = desc_mn_major(v_addr + st * TILE_BYTES + (u & 1) * (SUB * 128));
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-        } else {
+        for (int ks = 0; ks < 4; ++ks)
+          tc_mma_ts(tb + COL_O, tb + COL_S + (u & 1) * SUB + ks * 8, vd + ks * (2048 >> 4), IDESC_PV, (u | ks) != 0);
+        tc_commit(&bars.o_done[x]);
+        if ((u & 1) || u == n_mine - 1) tc_commit(&bars.v_empty[x][st]);
+      }
+      __syncwarp();
+      if (x == 0) TC_STAMP(1, u, 2);
+      if (u + 2 < n_mine) {
+        wait_k(u + 2);
+        if (!ok) break;
+        issue_qk(u + 2);
+      }
+      if (x == 0) TC_STAMP(1, u, 3);
+    }
+  } else if (warp >= 4) {
+    // ---------------- softmax: warps 4-7 take query tile 0, warps 8-11 query tile 1; one thread per row
+    const int x = (warp - 4) >> 2;
+    const int qd = warp & 3;                                 // this warp's quarter of the 128 lanes
+    const int row = qd * 32 + lane;
+    const int t0x = t0 + x * tpt, t1x = min(q_len, t0x + tpt);
+    const int tok = t0x + row / G;
+    const int p = tok < t1x ? p_first + tok : NO_ROW;
+    const int row_lo = window > 0 ? p - window + 1 : 0;
+    const int lox = window > 0 ? max(0, p_first + t0x - window + 1) : 0, hix = p_first + t1x - 1;
+    const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16) + x * COLS_PER_TILE;
+    uint64_t* o_done = &bars.o_done[x];
+    const int n_mine = x ? n_x[1] : n_x[0];
+    const bool stamp = (threadIdx.x & 127) == 64;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int u = 0; u < n_mine && ok; ++u) {
+      const int h = u & 1;
+      ok = __all_sync(0xffffffffu, tc_mbar_wait(&bars.s_full[x][h], (u >> 1) & 1, abort_flag, err, 15)) != 0;    // warp-uniform
+      if (!ok) break;
+      tc_fence_after();
+      if (stamp) TC_STAMP(2 + x, u, 0);
+      const int key0 = T0 + u * SUB;
+      const uint32_t s_addr = lane_addr + COL_S + h * SUB;
+      // a half every key of which every row of the query tile sees needs no masking (rows past the request's tokens
+      // are computed like the others and never stored)
+      const bool interior = key0 >= lox && key0 + SUB - 1 <= min(hix, p_first + t0x) && (window == 0 || key0 >= hix - window + 1);
+      // the row's 64 scores into registers with one wait
+      uint32_t v[2][32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) tc_ld32(s_addr + c * 32, v[c]);
+      tc_wait_ld();
+      if (stamp) TC_STAMP(2 + x, u, 1);
+      // the row's maximum over the visible keys, four chains
+      float mxc[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (interior) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mxc[(c << 1) | (i & 1)] = fmaxf(mxc[(c << 1) | (i & 1)], __uint_as_float(v[c][i]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int key = key0 + c * 32 + i;
-            const bool vis = key <= p && key >= row_lo && key >= lo && key <= hi;
-            if (vis) mx = fmaxf(mx, __uint_as_float(v[i]));
+            const bool vis = key <= p && key >= row_lo && key >= lox && key <= hix;
+            if (vis) mxc[(c << 1) | (i & 1)] = fmaxf(mxc[(c << 1) | (i & 1)], __uint_as_float(v[c][i]));
           }
-        }
       }
-      mx *= scale_log2;                                        // the scale is positive: the maximum commutes with it
+      const float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3])) * scale_log2;   // the scale is positive
       // keep the old reference maximum unless the new one is more than 2^8 above it (warp-uniform decision,
       // since the tensor-memory loads and stores of the rescaling are warp-wide)
       const float m_new = fmaxf(m_used, mx);
@@ -302,82 +404,83 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         m_used = m_new;
       }
       const float ref = m_used == -INFINITY ? 0.f : m_used;
-      if (j > 0) {
-        // the previous tile's P V must have landed in O before O is rescaled or P is overwritten
-        ok = __all_sync(0xffffffffu, tc_mbar_wait(&o_done, (j - 1) & 1, abort_flag, err, 16)) != 0;
+      if (stamp) TC_STAMP(2 + x, u, 2);
+      if (u > 0 && any_grow) {
+        // O is rescaled between the previous half's P V, which must have landed, and this half's, which waits for P
+        ok = __all_sync(0xffffffffu, tc_mbar_wait(o_done, (u - 1) & 1, abort_flag, err, 16)) != 0;
         if (!ok) break;
         tc_fence_after();
-        if (any_grow) {
-          l *= factor;
+        l *= factor;
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v[32];
-            tc_ld32(lane_addr + COL_O + c * 32, v);
-            tc_wait_ld();
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[16];
+          tc_ld16(lane_addr + COL_O + c * 16, o);
+          tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
-            tc_st32(lane_addr + COL_O + c * 32, v);
-          }
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tc_st16(lane_addr + COL_O + c * 16, o);
         }
       }
-      // pass 2: p = 2^(s - ref), the row sum, and P as bfloat16 pairs.  P goes over the part of S already read: the
-      // 16 columns of chunk c lie below column 32 (c + 1).
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32], pk[16];
-        tc_ld32(lane_addr + COL_S + c * 32, v);
-        tc_wait_ld();
+      // p = 2^(s - ref), the row sum, and P as bfloat16 pairs over the first 32 columns of this score buffer (its
+      // scores are all in registers by now)
+      float lc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
         if (interior) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float e0 = tc_exp2(fmaf(__uint_as_float(v[i]), scale_log2, -ref));
-            const float e1 = tc_exp2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -ref));
-            l += e0 + e1;
+            const float e0 = tc_exp2(fmaf(__uint_as_float(v[c][i]), scale_log2, -ref));
+            const float e1 = tc_exp2(fmaf(__uint_as_float(v[c][i + 1]), scale_log2, -ref));
+            lc[i & 2] += e0; lc[(i & 2) + 1] += e1;
             pk[i >> 1] = tc_pack(e0, e1);
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const int key = key0 + c * 32 + i;
-            const bool v0 = key <= p && key >= row_lo && key >= lo && key <= hi;
-            const bool v1 = key + 1 <= p && key + 1 >= row_lo && key + 1 >= lo && key + 1 <= hi;
-            const float e0 = v0 ? tc_exp2(fmaf(__uint_as_float(v[i]), scale_log2, -ref)) : 0.f;
-            const float e1 = v1 ? tc_exp2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -ref)) : 0.f;
-            l += e0 + e1;
+            const bool v0 = key <= p && key >= row_lo && key >= lox && key <= hix;
+            const bool v1 = key + 1 <= p && key + 1 >= row_lo && key + 1 >= lox && key + 1 <= hix;
+            const float e0 = v0 ? tc_exp2(fmaf(__uint_as_float(v[c][i]), scale_log2, -ref)) : 0.f;
+            const float e1 = v1 ? tc_exp2(fmaf(__uint_as_float(v[c][i + 1]), scale_log2, -ref)) : 0.f;
+            lc[i & 2] += e0; lc[(i & 2) + 1] += e1;
             pk[i >> 1] = tc_pack(e0, e1);
           }
         }
-        tc_st16(lane_addr + COL_P + c * 16, pk);
+        tc_st16(s_addr + c * 16, pk);
       }
+      l += (lc[0] + lc[1]) + (lc[2] + lc[3]);
+      if (stamp) TC_STAMP(2 + x, u, 3);
       tc_wait_st();
       tc_fence_before();
-      tc_mbar_arrive(&p_ready);
+      tc_mbar_arrive(&bars.p_ready[x][h]);
+      if (stamp) TC_STAMP(2 + x, u, 4);
     }
-    if (ok && n_tiles > 0) {
-      ok = __all_sync(0xffffffffu, tc_mbar_wait(&o_done, (n_tiles - 1) & 1, abort_flag, err, 17)) != 0;
+    if (ok && n_mine > 0) {
+      ok = __all_sync(0xffffffffu, tc_mbar_wait(o_done, (n_mine - 1) & 1, abort_flag, err, 17)) != 0;
       if (ok) {
         tc_fence_after();
         const float inv = l > 0.f ? 1.f / l : 0.f;
         bf16* dst = p != NO_ROW ? out + ((size_t)(q0 + tok) * nq + kvh * G + row % G) * D : nullptr;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tc_ld32(lane_addr + COL_O + c * 32, v);
+          uint32_t o[32];
+          tc_ld32(lane_addr + COL_O + c * 32, o);
           tc_wait_ld();
           if (dst) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 pk;
-              pk.x = tc_pack(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-              pk.y = tc_pack(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-              pk.z = tc_pack(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-              pk.w = tc_pack(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+              pk.x = tc_pack(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              pk.y = tc_pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              pk.z = tc_pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              pk.w = tc_pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
               *reinterpret_cast<uint4*>(dst + c * 32 + i) = pk;
             }
           }
         }
       }
-    } else if (n_tiles == 0 && p != NO_ROW) {
+    } else if (n_mine == 0 && p != NO_ROW) {
       bf16* dst = out + ((size_t)(q0 + tok) * nq + kvh * G + row % G) * D;
       for (int i = 0; i < D; ++i) dst[i] = __float2bfloat16_rn(0.f);
     }
@@ -392,6 +495,12 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
 }
+
+#ifdef TC_TRACE
+IFB_EXPORT int ifb_attention_tc_trace(long long* host) {
+  return cudaMemcpyFromSymbol(host, tc_trace_buf, sizeof(tc_trace_buf)) == cudaSuccess ? IFB_OK : IFB_ERR_ARG;
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------------
 // qkv [n_tokens, row_stride] bfloat16 (the q heads are the first nq * 128 columns), pages [num_pages, 2, nkv, page_size, 128],
@@ -429,7 +538,7 @@ IFB_EXPORT int ifb_attention_tc(const void* qkv, int row_stride, const void* pag
     if (e != cudaSuccess) return -(int)e;
     configured = true;
   }
-  const int tpc = ROWS / G;
+  const int tpc = 2 * (ROWS / G);                            // tokens per CTA: two query tiles
   dim3 grid((max_q_len + tpc - 1) / tpc, nkv, n_req);
   attn_tile_tc_kernel<<<grid, TC_THREADS, SMEM_BYTES, stream>>>(q_map, kv_map, (int)rows, err, block_tables, bt_stride, cu_q, seq_lens,
                                                                 (bf16*)out, nq, nkv, page_size, scale * 1.4426950408889634f, window);

@@ -95,6 +95,7 @@ class StepContext:
         self.num_logit_rows = 0
         self.max_logit_rows = runner.max_tokens
         self.max_q_len = 0
+        self.min_q_len = 1
         self.max_seq_len = 0
         self.token_ids = self.positions = self.cu_q = self.seq_lens = None
         self.state_slots = self.first_portion = self.logit_rows = self.req_index = None
@@ -307,7 +308,8 @@ class ModelRunner:
             ctx = self._build_context(entries, pad_to=r_bucket, seq_bucket=seq_bucket, **build)
         else:
             ctx = self._build_context(entries, seq_bucket=seq_bucket, **build)
-            key = ("any", ctx.num_tokens, ctx.num_requests, ctx.num_logit_rows, ctx.max_q_len, seq_bucket, sample, greedy)
+            key = ("any", ctx.num_tokens, ctx.num_requests, ctx.num_logit_rows, ctx.max_q_len, ctx.min_q_len, seq_bucket,
+                   sample, greedy)
         self._apply_feed(ctx, feed)
         stamp = (self.arena.generation, getattr(self.rt.kernels, "scratch_generation", 0))
         held = self._graphs.get(key)
@@ -367,7 +369,7 @@ class ModelRunner:
         np_small, np_tables = self._stage_np[turn]
         ids, pos, req, rows, cu, seq, slots, first = [], [], [], [], [0], [], [], []
         group_slots = [[] for _ in cache.kv_groups]
-        max_q = 0
+        max_q, min_q = 0, 1 << 30
         for r, e in enumerate(entries):
             start = cache.num_computed(e.request_id)
             n = len(e.tokens)
@@ -380,7 +382,7 @@ class ModelRunner:
             seq.append(start + n)
             slots.append(cache.slot_of(e.request_id))
             first.append(1 if start == 0 else 0)
-            max_q = max(max_q, n)
+            max_q, min_q = max(max_q, n), min(min_q, n)
             for gi in range(len(cache.kv_groups)):
                 group_slots[gi].extend(cache.slots_for(e.request_id, gi, n))
                 row = self._table_row(e.request_id, gi)
@@ -431,6 +433,7 @@ class ModelRunner:
         ctx = StepContext(self)
         ctx.num_tokens, ctx.num_requests, ctx.num_logit_rows = N, R, M
         ctx.max_q_len, ctx.max_seq_len = max_q, max(max(seq), seq_bucket)
+        ctx.min_q_len = 1 if pad_to > len(entries) else max(1, min(min_q, max_q))
         df = d.view(torch.float32)
         ctx.temperatures, ctx.uniforms = df[o_f:o_f + r_max], df[o_f + r_max:o_f + 2 * r_max]
         ctx.num_real_logit_rows = real_rows

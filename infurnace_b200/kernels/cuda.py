@@ -260,7 +260,7 @@ class CudaKernels:
 
     # ------------------------------------------------------------------ attention
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out,
-                        scale, window, max_q_len, max_seq_len):
+                        scale, window, max_q_len, max_seq_len, min_q_len=1):
         _dense(qkv, "qkv"), _dense(kv_pages, "kv_pages", qkv.dtype), _dense(out, "out", qkv.dtype)
         _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
         if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
@@ -276,7 +276,8 @@ class CudaKernels:
         if qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and group <= 16 \
                 and num_heads % num_kv_heads == 0:
             return self._paged_attention_mma(qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q,
-                                             seq_lens, out, scale, window, max_q_len, max_seq_len, n, r)
+                                             seq_lens, out, scale, window, max_q_len, max_seq_len, n, r,
+                                             min_q_len=min_q_len)
         self.launches += 1
         _check(self.core.ifb_paged_attention_simt(
             qkv.data_ptr(), _code(qkv), qkv.stride(0), kv_pages.data_ptr(), block_tables.data_ptr(),
@@ -328,7 +329,7 @@ class CudaKernels:
         return self._attn_scratch
 
     def _paged_attention_mma(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out,
-                             scale, window, max_q_len, max_seq_len, n, r, num_splits=None):
+                             scale, window, max_q_len, max_seq_len, n, r, num_splits=None, min_q_len=1):
         lib = self.attention_library(head_dim)
         group = num_heads // num_kv_heads
         only_small = max_q_len * group <= 16
@@ -349,6 +350,8 @@ class CudaKernels:
         if use_tc:
             self._attention_tc(qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out, scale,
                                window, max_q_len, n, r)
+            if min_q_len * group > 16:
+                return                 # no request of this step is left for the small-q kernel
             only_small = True          # the tile kernel's requests are done; the small-q kernel takes the rest
         self.launches += 1 + (0 if only_small else 1)
         if self._dev_err is None:

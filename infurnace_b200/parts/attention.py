@@ -58,7 +58,8 @@ class PagedAttention:
                                      None, 0, False, ctx.positions, slots, kv.pages)
         attn = ctx.buffer("attn", (n, s.num_heads * s.head_dim), self.rt.act_dtype)
         k.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, kv.pages, kv.block_tables,
-                          ctx.cu_q, ctx.seq_lens, attn, s.scale, s.window or 0, ctx.max_q_len, ctx.max_seq_len)
+                          ctx.cu_q, ctx.seq_lens, attn, s.scale, s.window or 0, ctx.max_q_len, ctx.max_seq_len,
+                          min_q_len=ctx.min_q_len)
         delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
         k.linear(attn, self.w_o, delta)
         return delta

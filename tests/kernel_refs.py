@@ -119,7 +119,7 @@ class ReferenceKernels:
 
     # ------------------------------------------------------------------ attention over pages
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q,
-                        seq_lens, out, scale, window, max_q_len, max_seq_len):
+                        seq_lens, out, scale, window, max_q_len, max_seq_len, min_q_len=1):
         """For request r the query tokens are rows cu_q[r] .. cu_q[r+1]-1 of qkv (their q
         heads are the first nq*d columns); the last of them stands at position
         seq_lens[r]-1.  A query at position p attends to the keys at positions
