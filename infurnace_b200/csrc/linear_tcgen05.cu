@@ -31,9 +31,11 @@ constexpr int G_THREADS = 192;
 constexpr uint32_t G_SPIN_LIMIT = 1u << 22;
 constexpr int G_TILE_BYTES = G_BM * G_BK * 2;   // 16 KB, same for an x tile and a w tile
 
-template <int EPI> struct GemmCfg {
+// DEEP: the grid has no more CTAs than the device has SMs, so a CTA has the SM's shared memory to itself and keeps
+// twice as many stages in flight (what hides the latency of the loads when no second CTA does).
+template <int EPI, int DEEP> struct GemmCfg {
   static constexpr int NB = EPI ? 2 : 1;                      // w tiles per stage
-  static constexpr int STAGES = EPI ? 2 : 3;                  // 2 x 48 KB or 3 x 32 KB: two CTAs per SM either way
+  static constexpr int STAGES = (EPI ? 2 : 3) * (DEEP ? 2 : 1);   // 2 x 48 KB or 3 x 32 KB: two CTAs per SM; DEEP: one
   static constexpr int STAGE_BYTES = (1 + NB) * G_TILE_BYTES;
   static constexpr int TMEM_COLS = NB * G_BN;                 // 128 or 256 columns of 32 bits
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
@@ -73,6 +75,13 @@ __device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinq
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, int cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
 }
+// True in exactly one lane of a converged warp.  Code under it is known to the compiler as single-threaded, which lets
+// it keep the descriptors of the copies and products it issues in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -102,11 +111,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 // Instruction descriptor: float32 accumulator, bfloat16 a and b, both K-major, N = 128, M = 128.
 constexpr uint32_t G_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(G_BN >> 3) << 17) | ((uint32_t)(G_BM >> 4) << 24);
 
-template <int EPI, typename TO>
+template <int EPI, int DEEP, typename TO>
 __global__ void __launch_bounds__(G_THREADS)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                       TO* __restrict__ out, int n_rows, int o_out, int k_dim, int* __restrict__ err) {
-  using Cfg = GemmCfg<EPI>;
+  using Cfg = GemmCfg<EPI, DEEP>;
   extern __shared__ unsigned char g_smem_raw[];
   const uint32_t raw = g_smem_u32(g_smem_raw);
   unsigned char* smem = g_smem_raw + (((raw + 1023u) & ~1023u) - raw);      // tiles need 1024-byte alignment
@@ -115,7 +124,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   uint64_t* accum = empty + Cfg::STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;     // warp-uniform
   const int m0 = blockIdx.y * G_BM, n0 = blockIdx.x * G_BN;
   const int kblocks = (k_dim + G_BK - 1) / G_BK;
 
@@ -133,27 +142,29 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
-      for (int kb = 0; kb < kblocks; ++kb) {
-        const int s = kb % Cfg::STAGES;
-        const uint32_t ph = (kb / Cfg::STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, err, 1)) break;
+    // the whole warp walks the stages and waits; one elected lane issues the copies
+    for (int kb = 0; kb < kblocks; ++kb) {
+      const int s = kb % Cfg::STAGES;
+      const uint32_t ph = (kb / Cfg::STAGES) & 1;
+      if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, err, 1)) break;
+      if (elect_one()) {
         unsigned char* stage = smem + s * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
         tma_load_2d(stage, &tmap_x, &full[s], kb * G_BK, m0);
         tma_load_2d(stage + G_TILE_BYTES, &tmap_w, &full[s], kb * G_BK, n0);
         if (EPI) tma_load_2d(stage + 2 * G_TILE_BYTES, &tmap_w, &full[s], kb * G_BK, o_out + n0);
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      bool ok = true;
-      for (int kb = 0; kb < kblocks && ok; ++kb) {
-        const int s = kb % Cfg::STAGES;
-        const uint32_t ph = (kb / Cfg::STAGES) & 1;
-        ok = mbar_wait(&full[s], ph, abort_flag, err, 2);
-        if (!ok) break;
-        tc_fence_after();
+    bool ok = true;
+    for (int kb = 0; kb < kblocks && ok; ++kb) {
+      const int s = kb % Cfg::STAGES;
+      const uint32_t ph = (kb / Cfg::STAGES) & 1;
+      ok = mbar_wait(&full[s], ph, abort_flag, err, 2);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
         const uint32_t a_addr = g_smem_u32(smem + s * Cfg::STAGE_BYTES);
         const uint64_t a_desc = make_smem_desc(a_addr);
         const uint64_t b_desc = make_smem_desc(a_addr + G_TILE_BYTES);
@@ -166,8 +177,9 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           if (EPI) umma_bf16(tmem_base + G_BN, a_desc + step, b2_desc + step, G_IDESC, acc);
         }
         umma_commit(&empty[s]);
+        if (kb == kblocks - 1) umma_commit(accum);
       }
-      if (ok) umma_commit(accum);
+      __syncwarp();
     }
   } else {
     const int q = warp & 3;                                      // this warp's quarter of the 128 lanes
@@ -239,18 +251,31 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int k, int box_ro
   return ifb_tensor_map_bf16(m, ptr, 2, dims, strides, box);
 }
 
-template <int EPI, typename TO>
-static int tc_launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int n, int o, int k, int* err, cudaStream_t s) {
-  using Cfg = GemmCfg<EPI>;
+template <int EPI, int DEEP, typename TO>
+static int tc_launch_cfg(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int n, int o, int k, int* err, dim3 grid,
+                         cudaStream_t s) {
+  using Cfg = GemmCfg<EPI, DEEP>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_kernel<EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_kernel<EPI, DEEP, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return -(int)e;
     configured = true;
   }
-  dim3 grid((o + G_BN - 1) / G_BN, (n + G_BM - 1) / G_BM);
-  linear_tcgen05_kernel<EPI, TO><<<grid, G_THREADS, Cfg::SMEM_BYTES, s>>>(mx, mw, (TO*)out, n, o, k, err);
+  linear_tcgen05_kernel<EPI, DEEP, TO><<<grid, G_THREADS, Cfg::SMEM_BYTES, s>>>(mx, mw, (TO*)out, n, o, k, err);
   return ifb_launch_status();
+}
+
+template <int EPI, typename TO>
+static int tc_launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int n, int o, int k, int* err, cudaStream_t s) {
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      sm_count = 1;
+  }
+  dim3 grid((o + G_BN - 1) / G_BN, (n + G_BM - 1) / G_BM);
+  if ((long long)grid.x * grid.y <= sm_count) return tc_launch_cfg<EPI, 1, TO>(mx, mw, out, n, o, k, err, grid, s);
+  return tc_launch_cfg<EPI, 0, TO>(mx, mw, out, n, o, k, err, grid, s);
 }
 
 // x [n_rows, k] and w [out_features (x2 for the silu_gate epilogue), k] bfloat16, 16-byte aligned, k a multiple of 8;
