@@ -3,19 +3,27 @@
 // brought to shared memory by TMA (128-byte swizzle), the accumulator in tensor memory, read back with
 // tcgen05.ld for the epilogue.
 //
-// One CTA per 128 x 128 output tile (tokens x features), 192 threads:
-//   warp 0, one thread: TMA producer.  Per 64-wide k block it waits for a free stage, arms the stage's
-//           "full" barrier with the byte count and issues the loads of the x tile and the w tile(s).
-//   warp 1, one thread: MMA issuer.  It waits for "full", issues four k=16 MMAs per tile and commits them
-//           to the stage's "empty" barrier, so the stage is reused as soon as the tensor core has read it.
-//           After the last k block it commits to the "accumulator ready" barrier.  Warp 1 also owns the
-//           allocation of tensor memory.
-//   warps 2-5: epilogue.  Each reads its quarter of the accumulator's 128 lanes (one token per thread),
-//           applies the epilogue and stores the row piece.
+// A CTA of 320 threads takes one output tile:
+//   warp 0: TMA producer.  Per 64-wide k block it waits for a free stage, arms the stage's "full" barrier with
+//           the byte count and issues the loads of the x tile and the w tile(s).
+//   warp 1: MMA issuer.  It waits for "full", issues the k=16 MMAs of the stage and commits them to the stage's
+//           "empty" barrier, so the stage is reused as soon as the tensor core has read it.  After the last
+//           k block it commits to the "accumulator ready" barrier.  Warp 1 also owns the tensor memory.
+//   warps 2-9: epilogue.  A warp reads its quarter (warp index mod 4) of the accumulator's 128 lanes, one token per
+//           thread and half; warps 2-5 take the first half of the tile's features and warps 6-9 the second.
+// In warps 0 and 1 all lanes wait and one elected lane issues.
 // Rows, features or k beyond the matrices are zero-filled by TMA and dropped at the store.
 //
-// Epilogue 1 (silu_gate): w holds gate rows [0, O) and up rows [O, 2O); a stage carries both w tiles, the
-// accumulator has two halves of 128 columns, and out = silu(gate) * up.
+// Tile shapes (GemmCfg): MH halves of 128 tokens share the w tile of a stage; each half accumulates NACC
+// columns in tensor memory with one MMA of N = NACC per k step.
+//   narrow  MH 1, NACC 128: 128 tokens x 128 features, 3 stages of 32 KB, two CTAs per SM;
+//   deep    the same with 6 stages, for grids of at most one CTA per SM (o and down projections of prompts of
+//           a few thousand tokens): the stages in flight are what hides the latency of the loads;
+//   wide    MH 2, NACC 256: 256 tokens x 256 features, 3 stages of 64 KB, all 512 columns of tensor memory:
+//           half the bytes from L2 per product of the narrow shape.
+// Epilogue 1 (silu_gate): w holds gate rows [0, O) and up rows [O, 2O).  A stage carries a gate tile and an up
+// tile back to back as one B operand, the accumulator's first NACC/2 columns are gate and the rest up, and
+// out = silu(gate) * up has NACC/2 features per CTA (narrow: NACC 256).
 //
 // Every wait on a barrier is bounded: after G_SPIN_LIMIT polls the thread writes a code to `*err`, raises
 // the CTA's abort flag, and everything falls through to the common exit, which frees the tensor memory.
@@ -23,22 +31,23 @@
 #include "common.cuh"
 
 typedef __nv_bfloat16 bf16;
-constexpr int G_BM = 128;          // tokens per tile  (MMA M)
-constexpr int G_BN = 128;          // features per tile (MMA N)
+constexpr int G_BM = 128;          // tokens per half tile (MMA M)
 constexpr int G_BK = 64;           // k per stage: 128 bytes, one swizzle row
 constexpr int G_UK = 16;           // k per MMA
-constexpr int G_THREADS = 192;
+constexpr int G_THREADS = 320;      // producer warp, MMA warp, eight epilogue warps
 constexpr uint32_t G_SPIN_LIMIT = 1u << 22;
-constexpr int G_TILE_BYTES = G_BM * G_BK * 2;   // 16 KB, same for an x tile and a w tile
+constexpr int G_TILE_BYTES = G_BM * G_BK * 2;   // 16 KB: 128 rows of one k block
 
-// DEEP: the grid has no more CTAs than the device has SMs, so a CTA has the SM's shared memory to itself and keeps
-// twice as many stages in flight (what hides the latency of the loads when no second CTA does).
-template <int EPI, int DEEP> struct GemmCfg {
-  static constexpr int NB = EPI ? 2 : 1;                      // w tiles per stage
-  static constexpr int STAGES = (EPI ? 2 : 3) * (DEEP ? 2 : 1);   // 2 x 48 KB or 3 x 32 KB: two CTAs per SM; DEEP: one
-  static constexpr int STAGE_BYTES = (1 + NB) * G_TILE_BYTES;
-  static constexpr int TMEM_COLS = NB * G_BN;                 // 128 or 256 columns of 32 bits
+template <int EPI_, int MH_, int NACC_, int STAGES_> struct GemmCfg {
+  static constexpr int EPI = EPI_, MH = MH_, NACC = NACC_, STAGES = STAGES_;
+  static constexpr int FO = EPI ? NACC / 2 : NACC;            // output features per CTA
+  static constexpr int A_BYTES = MH * G_TILE_BYTES;           // x rows of a stage
+  static constexpr int B_BYTES = NACC * G_BK * 2;             // w rows of a stage
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = MH * NACC;                 // 128, 256 or 512 columns of 32 bits
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+  // float32 accumulator, bfloat16 a and b, both K-major, M = 128, N = NACC
+  static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NACC >> 3) << 17) | ((uint32_t)(G_BM >> 4) << 24);
 };
 
 __device__ __forceinline__ uint32_t g_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -101,6 +110,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128 bytes, groups of 8
@@ -108,14 +127,19 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-// Instruction descriptor: float32 accumulator, bfloat16 a and b, both K-major, N = 128, M = 128.
-constexpr uint32_t G_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(G_BN >> 3) << 17) | ((uint32_t)(G_BM >> 4) << 24);
+#ifdef G_TRACE
+// Timestamps of the phases of CTA (0, 0), for tuning builds only.
+__device__ long long g_trace_buf[16];
+#define G_STAMP(k) do { if (blockIdx.x == 0 && blockIdx.y == 0) g_trace_buf[k] = clock64(); } while (0)
+#else
+#define G_STAMP(k) do {} while (0)
+#endif
 
-template <int EPI, int DEEP, typename TO>
+template <typename Cfg, typename TO>
 __global__ void __launch_bounds__(G_THREADS)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                       TO* __restrict__ out, int n_rows, int o_out, int k_dim, int* __restrict__ err) {
-  using Cfg = GemmCfg<EPI, DEEP>;
+  constexpr int EPI = Cfg::EPI, MH = Cfg::MH, NACC = Cfg::NACC, FO = Cfg::FO;
   extern __shared__ unsigned char g_smem_raw[];
   const uint32_t raw = g_smem_u32(g_smem_raw);
   unsigned char* smem = g_smem_raw + (((raw + 1023u) & ~1023u) - raw);      // tiles need 1024-byte alignment
@@ -125,8 +149,9 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;     // warp-uniform
-  const int m0 = blockIdx.y * G_BM, n0 = blockIdx.x * G_BN;
+  const int m0 = blockIdx.y * (MH * G_BM), n0 = blockIdx.x * FO;
   const int kblocks = (k_dim + G_BK - 1) / G_BK;
+  if (threadIdx.x == 0) G_STAMP(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -140,9 +165,9 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) G_STAMP(1);
 
   if (warp == 0) {
-    // the whole warp walks the stages and waits; one elected lane issues the copies
     for (int kb = 0; kb < kblocks; ++kb) {
       const int s = kb % Cfg::STAGES;
       const uint32_t ph = (kb / Cfg::STAGES) & 1;
@@ -150,9 +175,9 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       if (elect_one()) {
         unsigned char* stage = smem + s * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-        tma_load_2d(stage, &tmap_x, &full[s], kb * G_BK, m0);
-        tma_load_2d(stage + G_TILE_BYTES, &tmap_w, &full[s], kb * G_BK, n0);
-        if (EPI) tma_load_2d(stage + 2 * G_TILE_BYTES, &tmap_w, &full[s], kb * G_BK, o_out + n0);
+        tma_load_2d(stage, &tmap_x, &full[s], kb * G_BK, m0);                               // MH * 128 rows of x
+        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[s], kb * G_BK, n0);                // FO rows of w
+        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[s], kb * G_BK, o_out + n0);
       }
       __syncwarp();
     }
@@ -164,17 +189,20 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       ok = mbar_wait(&full[s], ph, abort_flag, err, 2);
       if (!ok) break;
       tc_fence_after();
+      if (lane == 0 && kb == 0) G_STAMP(2);
+      if (lane == 0 && kb == 1) G_STAMP(3);
+      if (lane == 0 && kb == kblocks - 1) G_STAMP(4);
       if (elect_one()) {
         const uint32_t a_addr = g_smem_u32(smem + s * Cfg::STAGE_BYTES);
         const uint64_t a_desc = make_smem_desc(a_addr);
-        const uint64_t b_desc = make_smem_desc(a_addr + G_TILE_BYTES);
-        const uint64_t b2_desc = make_smem_desc(a_addr + 2 * G_TILE_BYTES);
+        const uint64_t b_desc = make_smem_desc(a_addr + Cfg::A_BYTES);
 #pragma unroll
         for (int k = 0; k < G_BK / G_UK; ++k) {
           const uint64_t step = (uint64_t)((k * G_UK * 2) >> 4);          // 32 bytes per k step, in 16-byte units
           const uint32_t acc = (kb | k) != 0;
-          umma_bf16(tmem_base, a_desc + step, b_desc + step, G_IDESC, acc);
-          if (EPI) umma_bf16(tmem_base + G_BN, a_desc + step, b2_desc + step, G_IDESC, acc);
+#pragma unroll
+          for (int hf = 0; hf < MH; ++hf)
+            umma_bf16(tmem_base + hf * NACC, a_desc + (uint64_t)((hf * G_TILE_BYTES) >> 4) + step, b_desc + step, Cfg::IDESC, acc);
         }
         umma_commit(&empty[s]);
         if (kb == kblocks - 1) umma_commit(accum);
@@ -182,34 +210,52 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       __syncwarp();
     }
   } else {
+    // A warp's piece of the tile is 32 tokens (its lanes) by CW features.  A lane holds a token's row, so storing
+    // from registers would send the 32 lanes of a store to 32 different rows of `out`; the piece goes through shared
+    // memory instead (the stages, all consumed by now) and leaves in whole row segments, 512 bytes per store.
+    constexpr int CW = FO / 2;
+    // staged PW features at a time: all of the piece if eight warps' rows fit in the stages, else half of it
+    constexpr int PW = 8 * 32 * (CW * (int)sizeof(TO) + 16) <= Cfg::STAGES * Cfg::STAGE_BYTES ? CW : CW / 2;
+    constexpr int ROWB = PW * (int)sizeof(TO);                   // bytes of a row segment
+    constexpr int PITCH = ROWB + 16;                             // an odd number of 16-byte units: no bank conflicts
+    static_assert(8 * 32 * PITCH <= Cfg::STAGES * Cfg::STAGE_BYTES, "the staging rows must fit in the stages");
     const int q = warp & 3;                                      // this warp's quarter of the 128 lanes
-    const int row = m0 + q * 32 + lane;
+    const int c_lo = ((warp - 2) >> 2) * CW;                     // and its half of the tile's features
     if (mbar_wait(accum, 0, abort_flag, err, 3)) {
       tc_fence_after();
-      const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-      const bool vec = ((size_t)o_out * sizeof(TO)) % 16 == 0 && (((uintptr_t)out) & 15) == 0;
+      if (threadIdx.x == 64) G_STAMP(5);
+      const bool vec = ((size_t)o_out * sizeof(TO)) % 16 == 0 && (((uintptr_t)out) & 15) == 0 && n0 + c_lo + CW <= o_out;
+      unsigned char* buf = smem + (warp - 2) * (32 * PITCH);
 #pragma unroll 1
-      for (int c0 = 0; c0 < G_BN; c0 += 32) {
-        uint32_t v[32];
-        float y[32];
-        tmem_ld32(lane_base + c0, v);
-        if (EPI) {
-          uint32_t u[32];
-          tmem_ld32(lane_base + G_BN + c0, u);
-          tmem_ld_wait();
+      for (int hf = 0; hf < MH; ++hf) {
+        const int row0 = m0 + hf * G_BM + q * 32;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + hf * NACC;
+#pragma unroll 1
+       for (int p0 = c_lo; p0 < c_lo + CW; p0 += PW) {
+#pragma unroll 1
+        for (int c0 = p0; c0 < p0 + PW; c0 += 32) {
+          if (n0 + c0 >= o_out) break;                           // warp-uniform
+          uint32_t v[32];
+          float y[32];
+          tmem_ld32(lane_base + c0, v);
+          if (EPI) {
+            uint32_t u[32];
+            tmem_ld32(lane_base + FO + c0, u);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float g = __uint_as_float(v[j]);
-            y[j] = g / (1.f + expf(-g)) * __uint_as_float(u[j]);
+            for (int j = 0; j < 32; ++j) {
+              // silu(g) * u with the hardware's exp2 and reciprocal (relative error about 1e-6; the result is
+              // rounded to the output type)
+              const float g = __uint_as_float(v[j]);
+              y[j] = g * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * g)) * __uint_as_float(u[j]);
+            }
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
           }
-        } else {
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
-        }
-        if (row < n_rows) {
-          TO* dst = out + (size_t)row * o_out + n0 + c0;
-          if (vec && n0 + c0 + 32 <= o_out) {
+          if (vec) {
+            unsigned char* dst = buf + lane * PITCH + (c0 - p0) * (int)sizeof(TO);
             if (sizeof(TO) == 2) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
@@ -218,22 +264,36 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                 __nv_bfloat162 p2 = __floats2bfloat162_rn(y[j + 4], y[j + 5]), p3 = __floats2bfloat162_rn(y[j + 6], y[j + 7]);
                 pk.x = *reinterpret_cast<uint32_t*>(&p0); pk.y = *reinterpret_cast<uint32_t*>(&p1);
                 pk.z = *reinterpret_cast<uint32_t*>(&p2); pk.w = *reinterpret_cast<uint32_t*>(&p3);
-                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + j) = pk;
+                *reinterpret_cast<uint4*>(dst + j * 2) = pk;
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+                *reinterpret_cast<float4*>(dst + j * 4) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
             }
-          } else {
+          } else if (row0 + lane < n_rows) {
+            TO* dst = out + (size_t)(row0 + lane) * o_out + n0 + c0;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (n0 + c0 + j < o_out) dst[j] = from_f32<TO>(y[j]);
           }
         }
+        if (vec) {
+          __syncwarp();
+          unsigned char* obase = reinterpret_cast<unsigned char*>(out + (size_t)row0 * o_out + n0 + p0);
+#pragma unroll 4
+          for (int off = lane * 16; off < 32 * ROWB; off += 512) {
+            const int r = off / ROWB, cb = off % ROWB;
+            if (row0 + r < n_rows)
+              *reinterpret_cast<uint4*>(obase + (size_t)r * o_out * sizeof(TO) + cb) = *reinterpret_cast<const uint4*>(buf + r * PITCH + cb);
+          }
+          __syncwarp();                                          // before the next rows overwrite the buffer
+        }
+       }
       }
     }
   }
+  if (threadIdx.x == 64) G_STAMP(6);
   if (*abort_flag) {                         // a wait gave up: let copies in flight land before the CTA goes away
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
@@ -241,6 +301,12 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, Cfg::TMEM_COLS); }
 }
+
+#ifdef G_TRACE
+IFB_EXPORT int ifb_linear_tcgen05_trace(long long* host) {
+  return cudaMemcpyFromSymbol(host, g_trace_buf, sizeof(g_trace_buf)) == cudaSuccess ? IFB_OK : IFB_ERR_ARG;
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------------
 // A [rows, k] bfloat16 row-major matrix as a tensor map with boxes of 64 k x box_rows rows, 128-byte swizzle.
@@ -251,52 +317,67 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int k, int box_ro
   return ifb_tensor_map_bf16(m, ptr, 2, dims, strides, box);
 }
 
-template <int EPI, int DEEP, typename TO>
-static int tc_launch_cfg(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int n, int o, int k, int* err, dim3 grid,
-                         cudaStream_t s) {
-  using Cfg = GemmCfg<EPI, DEEP>;
+template <typename Cfg, typename TO>
+static int tc_launch_cfg(const void* x, const void* w, void* out, int n, int o, int k, int* err, cudaStream_t s) {
+  CUtensorMap mx, mw;
+  int st = make_map(&mx, x, n, k, Cfg::MH * G_BM);
+  if (st) return st;
+  st = make_map(&mw, w, Cfg::EPI ? 2 * o : o, k, Cfg::EPI ? Cfg::NACC / 2 : Cfg::NACC);
+  if (st) return st;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_kernel<EPI, DEEP, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_kernel<Cfg, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return -(int)e;
     configured = true;
   }
-  linear_tcgen05_kernel<EPI, DEEP, TO><<<grid, G_THREADS, Cfg::SMEM_BYTES, s>>>(mx, mw, (TO*)out, n, o, k, err);
+  dim3 grid((o + Cfg::FO - 1) / Cfg::FO, (n + Cfg::MH * G_BM - 1) / (Cfg::MH * G_BM));
+  if (grid.y > 65535) return IFB_ERR_SIZE;
+  linear_tcgen05_kernel<Cfg, TO><<<grid, G_THREADS, Cfg::SMEM_BYTES, s>>>(mx, mw, (TO*)out, n, o, k, err);
   return ifb_launch_status();
 }
 
+// The shape of the tiles: a wave of wide tiles does four 128 x 128 products per SM in little more time than a wave of
+// narrow tiles (two CTAs per SM) does two, but only if there are enough wide tiles to fill the SMs.  shape: 0 chooses,
+// 1 narrow, 2 deep, 3 wide (for tests and measurements).
 template <int EPI, typename TO>
-static int tc_launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int n, int o, int k, int* err, cudaStream_t s) {
+static int tc_launch(const void* x, const void* w, void* out, int n, int o, int k, int* err, int shape, cudaStream_t s) {
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       sm_count = 1;
   }
-  dim3 grid((o + G_BN - 1) / G_BN, (n + G_BM - 1) / G_BM);
-  if ((long long)grid.x * grid.y <= sm_count) return tc_launch_cfg<EPI, 1, TO>(mx, mw, out, n, o, k, err, grid, s);
-  return tc_launch_cfg<EPI, 0, TO>(mx, mw, out, n, o, k, err, grid, s);
+  using Narrow = GemmCfg<EPI, 1, EPI ? 256 : 128, EPI ? 2 : 3>;
+  using Deep = GemmCfg<EPI, 1, EPI ? 256 : 128, EPI ? 4 : 6>;
+  using Wide = GemmCfg<EPI, 2, 256, 3>;
+  if (shape == 0) {
+    const long long tn = (long long)((o + Narrow::FO - 1) / Narrow::FO) * ((n + G_BM - 1) / G_BM);
+    const long long tw = (long long)((o + Wide::FO - 1) / Wide::FO) * ((n + 2 * G_BM - 1) / (2 * G_BM));
+    const double cost_narrow = (double)((tn + 2 * sm_count - 1) / (2 * sm_count));
+    const double cost_wide = (double)((tw + sm_count - 1) / sm_count) * 1.15;
+    // (with the silu_gate epilogue a narrow tile already accumulates 256 columns per product, and measured faster)
+    shape = (!EPI && n > G_BM && cost_wide < cost_narrow) ? 3 : (tn <= sm_count ? 2 : 1);
+  }
+  if (shape == 3) return tc_launch_cfg<Wide, TO>(x, w, out, n, o, k, err, s);
+  if (shape == 2) return tc_launch_cfg<Deep, TO>(x, w, out, n, o, k, err, s);
+  return tc_launch_cfg<Narrow, TO>(x, w, out, n, o, k, err, s);
 }
 
 // x [n_rows, k] and w [out_features (x2 for the silu_gate epilogue), k] bfloat16, 16-byte aligned, k a multiple of 8;
-// out bfloat16 or float32.  `err` points to a device int that stays 0 unless a bounded wait gave up.
+// out bfloat16 or float32.  `err` points to a device int that stays 0 unless a bounded wait gave up.  shape: 0 lets the
+// library choose the tile shape, 1-3 force narrow, deep or wide.
 IFB_EXPORT int ifb_linear_tcgen05(const void* x, const void* w, void* out, int out_dtype, int n_rows, int out_features,
-                                  int k_dim, int epilogue, int* err, cudaStream_t stream) {
+                                  int k_dim, int epilogue, int* err, int shape, cudaStream_t stream) {
   if (n_rows <= 0 || out_features <= 0) return IFB_OK;
   if (k_dim < 8 || k_dim % 8) return IFB_ERR_SIZE;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return IFB_ERR_ALIGN;
   if (epilogue != 0 && epilogue != 1) return IFB_ERR_ARG;
-  if ((n_rows + G_BM - 1) / G_BM > 65535) return IFB_ERR_SIZE;
-  CUtensorMap mx, mw;
-  int st = make_map(&mx, x, n_rows, k_dim, G_BM);
-  if (st) return st;
-  st = make_map(&mw, w, epilogue ? 2 * out_features : out_features, k_dim, G_BN);
-  if (st) return st;
+  if (shape < 0 || shape > 3) return IFB_ERR_ARG;
   if (out_dtype == IFB_BF16)
-    return epilogue ? tc_launch<1, bf16>(mx, mw, out, n_rows, out_features, k_dim, err, stream)
-                    : tc_launch<0, bf16>(mx, mw, out, n_rows, out_features, k_dim, err, stream);
+    return epilogue ? tc_launch<1, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, stream)
+                    : tc_launch<0, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, stream);
   if (out_dtype == IFB_F32)
-    return epilogue ? tc_launch<1, float>(mx, mw, out, n_rows, out_features, k_dim, err, stream)
-                    : tc_launch<0, float>(mx, mw, out, n_rows, out_features, k_dim, err, stream);
+    return epilogue ? tc_launch<1, float>(x, w, out, n_rows, out_features, k_dim, err, shape, stream)
+                    : tc_launch<0, float>(x, w, out, n_rows, out_features, k_dim, err, shape, stream);
   return IFB_ERR_DTYPE;
 }

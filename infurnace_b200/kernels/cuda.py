@@ -158,17 +158,18 @@ class CudaKernels:
         _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
                                          n, o, k, epi, self._stream()), "linear")
 
-    def _linear_tcgen05(self, x, w, out, n, o, k, epi):
+    def _linear_tcgen05(self, x, w, out, n, o, k, epi, shape=0):
+        """shape: 0 lets the library choose its tile shape; 1 narrow, 2 deep, 3 wide."""
         if self._tc is None:
             self._tc = load_library("linear_tcgen05", progress=self._progress)
             self._tc.ifb_linear_tcgen05.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                    c_void_p, c_void_p]
+                                                    c_void_p, c_int, c_void_p]
         if self._dev_err is None:
             self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.launches += 1
         self._err_armed = True
         _check(self._tc.ifb_linear_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), n, o, k, epi,
-                                           self._dev_err.data_ptr(), self._stream()), "linear")
+                                           self._dev_err.data_ptr(), int(shape), self._stream()), "linear")
 
     def check_device_errors(self):
         """Raise if a kernel recorded that one of its bounded waits gave up (synchronises)."""

@@ -254,15 +254,17 @@ def test_linear_skinny(K, od, n, o, k, splits, epilogue):
 @pytest.mark.parametrize("n,o,k", [(128, 128, 64), (65, 72, 72), (300, 333, 136), (2048, 1024, 1024), (130, 200, 1000),
                                    (257, 4096, 3072), (1000, 151936 // 64, 520)])
 @pytest.mark.parametrize("epilogue", ["none", "silu_gate"])
-def test_linear_tcgen05(K, od, n, o, k, epilogue):
+@pytest.mark.parametrize("shape", [0, 1, 2, 3])
+def test_linear_tcgen05(K, od, n, o, k, epilogue, shape):
     """The many-rows product on tcgen05 (TMA in, tensor memory accumulator): tiles that hang over
-    the ends of all three dimensions, and both epilogues."""
+    the ends of all three dimensions, both epilogues, and each tile shape (0: the library's choice,
+    narrow, deep, wide)."""
     x = rnd((n, k), torch.bfloat16, 4)
     w = rnd((2 * o if epilogue == "silu_gate" else o, k), torch.bfloat16, 5, scale=k ** -0.5)
     ref = torch.empty((n, o), dtype=od)
     REF.linear(x, w, ref, epilogue)
     out = torch.full((n, o), float("nan"), dtype=od, device="cuda")
-    K._linear_tcgen05(x.cuda(), w.cuda(), out, n, o, k, 1 if epilogue == "silu_gate" else 0)
+    K._linear_tcgen05(x.cuda(), w.cuda(), out, n, o, k, 1 if epilogue == "silu_gate" else 0, shape=shape)
     K.check_device_errors()
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2 if od == torch.bfloat16 else 2e-4,
                                atol=2e-3 if od == torch.bfloat16 else 1e-4)
