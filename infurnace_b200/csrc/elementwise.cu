@@ -275,31 +275,46 @@ qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv
       for (int e = 0; e < EPL; ++e) sincosf(pos * inv_freq[(lane & 15) * EPL + e], &sn[e], &cs[e]);
     }
   }
-  for (int head = head0; head < min(heads, head0 + QK_HPW); ++head) {
+  // all of the block's heads are requested before the first is worked on: four loads in flight per lane
+  Vec in[QK_HPW];
+#pragma unroll
+  for (int hh = 0; hh < QK_HPW; ++hh)
+    if (head0 + hh < heads) in[hh] = *reinterpret_cast<const Vec*>(qkv + (size_t)tok * heads * d + (size_t)(head0 + hh) * d + lane * EPL);
+  // what does not depend on the head is computed once: the norm weights of this lane's elements and the token's
+  // place in the pages
+  float wq[EPL], wk[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    wq[e] = qw && head0 < nq ? load_as_f32(qw, w_dtype, lane * EPL + e) : 1.f;
+    wk[e] = kw && head0 + QK_HPW > nq && head0 < nq + nkv ? load_as_f32(kw, w_dtype, lane * EPL + e) : 1.f;
+  }
+  size_t page_base = 0;
+  if (slot >= 0) page_base = (size_t)(slot / page_size) * 2 * nkv * page_size + (slot % page_size);
+  const bool rotate = inv_freq != nullptr;
+#pragma unroll
+  for (int hh = 0; hh < QK_HPW; ++hh) {
+    const int head = head0 + hh;
+    if (head >= heads) continue;
     T* src = qkv + (size_t)tok * heads * d + (size_t)head * d + lane * EPL;
     const bool is_v = head >= nq + nkv, is_k = head >= nq && !is_v;
     T* dst = nullptr;
-    if (slot >= 0 && head >= nq) {
-      const int kvh = is_v ? head - nq - nkv : head - nq;
-      dst = pages + ((((size_t)(slot / page_size) * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + (slot % page_size)) * d + lane * EPL;
-    }
+    if (slot >= 0 && head >= nq)       // pages[page][k or v][kv head][place][d]
+      dst = pages + (page_base + (size_t)(is_v ? nkv + head - nq - nkv : head - nq) * page_size) * d + lane * EPL;
     if (is_v) {
-      if (dst) *reinterpret_cast<Vec*>(dst) = *reinterpret_cast<const Vec*>(src);
+      if (dst) *reinterpret_cast<Vec*>(dst) = in[hh];
       continue;
     }
-    const void* w = is_k ? kw : qw;
-    const bool rotate = inv_freq != nullptr;
-    if (!w && !rotate && !dst) continue;
-    const Vec in = *reinterpret_cast<const Vec*>(src);
+    const bool has_w = is_k ? kw != nullptr : qw != nullptr;
+    if (!has_w && !rotate && !dst) continue;
     float v[EPL];
     float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) { v[e] = to_f32<T>(in.v[e]); ss += v[e] * v[e]; }
-    if (w) {
+    for (int e = 0; e < EPL; ++e) { v[e] = to_f32<T>(in[hh].v[e]); ss += v[e] * v[e]; }
+    if (has_w) {
       ss = warp_sum(ss);
       const float r = rsqrtf(ss / (float)d + eps);
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) v[e] = v[e] * r * load_as_f32(w, w_dtype, lane * EPL + e);
+      for (int e = 0; e < EPL; ++e) v[e] = v[e] * r * (is_k ? wk[e] : wq[e]);
     }
     if (rotate) {
       const bool first = lane < 16;
@@ -312,7 +327,7 @@ qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv
     Vec res;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) res.v[e] = from_f32<T>(v[e]);
-    if (w || rotate) *reinterpret_cast<Vec*>(src) = res;
+    if (has_w || rotate) *reinterpret_cast<Vec*>(src) = res;
     if (dst) *reinterpret_cast<Vec*>(dst) = res;
   }
 }

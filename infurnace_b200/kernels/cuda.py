@@ -73,7 +73,10 @@ class CudaKernels:
                                       c_void_p]
         c.ifb_linear_skinny.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p]
-        c.ifb_linear_gemv.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        c.ifb_linear_gemv.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                      c_float, c_int, c_void_p]
+        c.ifb_linear_gemv_residual_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                    c_int, c_int, c_int, c_void_p]
         c.ifb_linear_skinny_scratch.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
         c.ifb_linear_skinny_scratch.restype = None
         self._lin_partials = None
@@ -140,13 +143,20 @@ class CudaKernels:
                                      self._stream()), "rmsnorm")
 
     # ------------------------------------------------------------------ matrix products
-    def linear(self, x, w, out, epilogue="none"):
+    def linear(self, x, w, out, epilogue="none", row_scale=None):
+        """out = x w^T with the epilogue.  ``row_scale`` (partials, parts, eps, width), from
+        :meth:`linear_residual_norm`, multiplies row n by rsqrt(sum_p partials[p, n] / width + eps)
+        before the epilogue; only where :meth:`can_fold_norm` says so."""
         _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
         n, k = x.shape
         o = out.shape[1]
         epi = {"none": 0, "silu_gate": 1}[epilogue]
         if w.shape[1] != k or out.shape[0] != n or w.shape[0] != (2 * o if epi else o):
             raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not match")
+        if row_scale is not None:
+            if not self.can_fold_norm(n, x.dtype, w) or out.dtype not in (torch.bfloat16, torch.float32):
+                raise KernelError("linear: a row scale is taken only by the few-rows bfloat16 kernel (see can_fold_norm)")
+            return self._linear_gemv(x, w, out, n, o, k, epi, row_scale)
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 \
                 and out.dtype in (torch.bfloat16, torch.float32):
             if n >= self.tc_min_rows:
@@ -180,10 +190,46 @@ class CudaKernels:
                 self._dev_err.zero_()
                 raise KernelError(f"a kernel gave up waiting on a barrier (code {code}); its output is not valid")
 
-    def _linear_gemv(self, x, w, out, n, o, k, epi):
+    def _linear_gemv(self, x, w, out, n, o, k, epi, row_scale=None):
         self.launches += 1
+        partials, parts, eps, width = row_scale if row_scale is not None else (None, 0, 0.0, 0)
+        if partials is not None:
+            _dense(partials, "row_scale partials", torch.float32)
+            if partials.dim() != 2 or partials.shape[0] < parts or partials.shape[1] != n:
+                raise KernelError("linear: row_scale partials must be [parts, rows]")
         _check(self.core.ifb_linear_gemv(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), n, o, k, epi,
-                                         self._stream()), "linear")
+                                         _ptr(partials), int(parts), float(eps), int(width), self._stream()), "linear")
+
+    # A norm folded into the products around it: RMSNorm(v) = v * g * r with one r per row, so the product that
+    # makes v writes v * g and partial sums of v^2, and the product that reads it multiplies by r at its end.
+    def can_fold_norm(self, n, dtype, w):
+        """Whether a product of ``n`` rows of ``dtype`` against ``w`` runs on the kernel that can
+        take or make a folded norm."""
+        return (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
+                and 0 < n <= self.gemv_max_rows)
+
+    def fold_parts(self, out_features):
+        """Partial sums per row that :meth:`linear_residual_norm` writes."""
+        return int(self.core.ifb_linear_gemv_parts(int(out_features)))
+
+    def linear_residual_norm(self, a, w, x, norm_weight, out, partials):
+        """x += a w^T (x float32, in place); out = x * norm_weight (bfloat16); partials[p, n] = the sum
+        of squares of row n of x over part p's features.  With ``linear(..., row_scale=(partials,
+        fold_parts(o), eps, o))`` after it this is x += a w^T followed by an RMSNorm of x."""
+        _dense(a, "a", torch.bfloat16), _dense(w, "w", torch.bfloat16), _dense(x, "x", torch.float32)
+        _dense(out, "out", torch.bfloat16), _dense(partials, "partials", torch.float32), _dense(norm_weight, "norm_weight")
+        n, k = a.shape
+        o = w.shape[0]
+        parts = self.fold_parts(o)
+        if w.shape[1] != k or x.shape != (n, o) or out.shape != (n, o) or norm_weight.numel() != o \
+                or partials.dim() != 2 or partials.shape[0] < parts or partials.shape[1] != n:
+            raise KernelError("linear_residual_norm: sizes of a, w, x, norm_weight, out and partials do not match")
+        if not self.can_fold_norm(n, a.dtype, w):
+            raise KernelError("linear_residual_norm: only for few rows of bfloat16 (see can_fold_norm)")
+        self.launches += 1
+        _check(self.core.ifb_linear_gemv_residual_norm(
+            a.data_ptr(), w.data_ptr(), x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight), out.data_ptr(),
+            partials.data_ptr(), n, o, k, self._stream()), "linear_residual_norm")
 
     def linear_splits(self, n, o, k):
         """CTAs that share the k range of one 64-feature tile: enough to cover the SMs twice, and

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..config.specs import AttentionSpec
-from .registry import build_part, register_part
+from .registry import build_part, fold_residual_norm, register_part, unfolded
 
 
 class PagedAttention:
@@ -36,11 +36,21 @@ class PagedAttention:
         self.position = build_part(spec.position, weights, runtime) if spec.position is not None else None
         self.qkv_width = (spec.num_heads + 2 * spec.num_kv_heads) * spec.head_dim
 
-    def forward(self, h, ctx, call):
+    can_fold_output = True
+
+    def can_take_folded(self, n):
+        can = getattr(self.k, "can_fold_norm", None)
+        return bool(can and can(n, self.rt.act_dtype, self.w_qkv))
+
+    def forward(self, h, ctx, call, fold=None):
         s, k = self.spec, self.k
+        h, row_scale = unfolded(h)
         n = h.shape[0]
         qkv = ctx.buffer("qkv", (n, self.qkv_width), self.rt.act_dtype)
-        k.linear(h, self.w_qkv, qkv)
+        if row_scale is not None:
+            k.linear(h, self.w_qkv, qkv, row_scale=row_scale)
+        else:
+            k.linear(h, self.w_qkv, qkv)
         kv = ctx.kv(call.cache)
         slots = kv.slot_mapping if call.store else None
         fused = self.position.fused_rotary() if self.position is not None else None
@@ -60,6 +70,9 @@ class PagedAttention:
         k.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, kv.pages, kv.block_tables,
                           ctx.cu_q, ctx.seq_lens, attn, s.scale, s.window or 0, ctx.max_q_len, ctx.max_seq_len,
                           min_q_len=ctx.min_q_len)
+        folded = fold_residual_norm(k, ctx, "mixer", attn, self.w_o, fold, self.rt.act_dtype)
+        if folded is not None:
+            return folded
         delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
         k.linear(attn, self.w_o, delta)
         return delta

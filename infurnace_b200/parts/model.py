@@ -64,8 +64,13 @@ class DecoderModel:
         x = ctx.buffer("x", (n, self.plan.hidden_size), torch.float32)
         self.embedding.forward(ctx.token_ids, x)
         pending = None
-        for call in self.schedule:
-            pending = self.layers[call.layer].forward(x, pending, ctx, call)
+        for i, call in enumerate(self.schedule):
+            layer = self.layers[call.layer]
+            nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+            if getattr(layer, "folds_norms", False) and getattr(nxt, "folds_norms", False):
+                pending = layer.forward(x, pending, ctx, call, next_layer=nxt)     # may hand over a folded norm
+            else:
+                pending = layer.forward(x, pending, ctx, call)
         m = ctx.num_logit_rows
         if m == 0:
             return None

@@ -12,6 +12,7 @@ class RMSNorm:
     (model.py:143,148) done in the same pass."""
 
     graph_safe = True     # launches depend on the step's sizes only, never on values read on the host
+    foldable = True       # weight and spec.eps are all that a neighbouring product needs to do this norm
 
     def __init__(self, spec: RMSNormSpec, weights, runtime):
         self.spec = spec

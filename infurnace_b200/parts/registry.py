@@ -18,6 +18,18 @@ Interfaces, by role:
                    ``pending`` (the previous block's last delta) to x before its first norm
                    and returns its own last delta instead of adding it
 * embedding:       ``forward(ids, out)``;  LM head: ``forward(h, out)``
+
+A norm folded into its neighbours (optional; a part without these attributes is simply
+given plain tensors and asked for plain deltas).  RMSNorm(v) = v * g * r with one number r
+per row, so the product that makes v can write v * g and partial sums of v^2, and the
+product that reads it can multiply its rows by r at the end: no kernel runs for the norm.
+
+* a norm with ``foldable = True`` exposes ``weight`` and ``spec.eps``;
+* a mixer or feed-forward with ``can_fold_output = True`` takes ``fold=(x, norm)`` and may
+  then add its result to x itself and return a :class:`Folded` for ``norm`` instead of a delta;
+* one with ``can_take_folded(n)`` true accepts a :class:`Folded` as ``h``;
+* a block with ``folds_norms = True`` takes ``next_layer=`` (the block that runs after it),
+  offers ``takes_folded(n)`` and accepts a :class:`Folded` as ``pending``.
 """
 from __future__ import annotations
 
@@ -39,6 +51,43 @@ def build_part(spec, weights, runtime):
     except KeyError:
         raise KeyError(f"no part registered for description type {type(spec).__name__}") from None
     return impl(spec, weights, runtime)
+
+
+class Folded:
+    """An activation whose RMSNorm is half done: ``values`` holds v * g in the activation
+    dtype and ``row_scale`` = (partials, parts, eps, width) is what a product needs to
+    finish it (``kernels.linear(..., row_scale=...)``)."""
+    __slots__ = ("values", "row_scale")
+
+    def __init__(self, values, row_scale):
+        self.values = values
+        self.row_scale = row_scale
+
+    @property
+    def shape(self):
+        return self.values.shape
+
+
+def unfolded(h):
+    """(tensor, row_scale or None) of a plain tensor or a :class:`Folded`."""
+    return (h.values, h.row_scale) if isinstance(h, Folded) else (h, None)
+
+
+def fold_residual_norm(kernels, ctx, tag, a, w, fold, act_dtype):
+    """The last product of a mixer or feed-forward with the residual addition and the next
+    norm folded in, if the kernels can do it for these sizes: returns a :class:`Folded`,
+    or None (then the caller runs the plain product).  ``fold`` = (x, norm)."""
+    if fold is None or not getattr(kernels, "can_fold_norm", None):
+        return None
+    x, norm = fold
+    n, o = a.shape[0], w.shape[0]
+    if a.dtype != act_dtype or x.shape != (n, o) or not kernels.can_fold_norm(n, a.dtype, w):
+        return None
+    parts = kernels.fold_parts(o)
+    out = ctx.buffer("folded_" + tag, (n, o), act_dtype)
+    partials = ctx.buffer("folded_partials_" + tag, (parts, n), __import__("torch").float32)
+    kernels.linear_residual_norm(a, w, x, norm.weight, out, partials)
+    return Folded(out, (partials, parts, float(norm.spec.eps), o))
 
 
 @dataclass

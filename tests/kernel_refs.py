@@ -18,8 +18,9 @@ import torch
 class ReferenceKernels:
     name = "reference"
 
-    def __init__(self, compute_dtype=torch.float32):
+    def __init__(self, compute_dtype=torch.float32, fold=True):
         self.cd = compute_dtype
+        self.fold = fold          # offer the folded norm (for few rows, as the CUDA kernels do)
 
     # ------------------------------------------------------------------ embedding
     def embed(self, table, ids, out):
@@ -50,16 +51,38 @@ class ReferenceKernels:
         out.copy_(y.to(out.dtype))
 
     # ------------------------------------------------------------------ matrix products
-    def linear(self, x, w, out, epilogue="none"):
+    def linear(self, x, w, out, epilogue="none", row_scale=None):
         """out = x @ w^T (w is [out_features, in_features]); accumulation in 32-bit.
         epilogue "silu_gate": w is [2I, K] with the gate rows first; out[n, j] =
-        silu(y[n, j]) * y[n, I + j]."""
+        silu(y[n, j]) * y[n, I + j].  row_scale (partials, parts, eps, width): row n of the
+        product is multiplied by rsqrt(sum_p partials[p, n] / width + eps) first."""
         y = x.to(self.cd) @ w.to(self.cd).t()
+        if row_scale is not None:
+            partials, parts, eps, width = row_scale
+            r = torch.rsqrt(partials[:parts].to(self.cd).sum(dim=0) / width + eps)
+            y = y * r[:, None]
         if epilogue == "silu_gate":
             half = y.shape[1] // 2
             g, u = y[:, :half], y[:, half:]
             y = g * torch.sigmoid(g) * u
         out.copy_(y.to(out.dtype))
+
+    def can_fold_norm(self, n, dtype, w):
+        return bool(self.fold) and 0 < n <= 64
+
+    def fold_parts(self, out_features):
+        return -(-out_features // 16)
+
+    def linear_residual_norm(self, a, w, x, norm_weight, out, partials):
+        """x += a @ w^T; out = x * norm_weight; partials[p, n] = sum of x[n, 16p:16p+16]^2."""
+        x.add_((a.to(self.cd) @ w.to(self.cd).t()).to(x.dtype))
+        v = x.to(self.cd)
+        out.copy_((v * norm_weight.to(self.cd)[None, :]).to(out.dtype))
+        o = v.shape[1]
+        parts = self.fold_parts(o)
+        sq = torch.zeros(v.shape[0], parts * 16, dtype=self.cd)
+        sq[:, :o] = v * v
+        partials[:parts].copy_(sq.view(v.shape[0], parts, 16).sum(dim=2).t().to(partials.dtype))
 
     # ------------------------------------------------------------------ q/k norm, rotation, store
     def rope_table(self, positions, inv_freq, out):

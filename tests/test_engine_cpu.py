@@ -42,6 +42,39 @@ def test_cutting_modes_on_the_host_path(models, name, mode):
         assert (out[rid] - P.forward(cfg, w, toks)).abs().max() < 2e-5, (rid, mode)
 
 
+def test_a_norm_folded_into_its_neighbours_changes_no_logit(models):
+    """Steps of few tokens leave the norms between products to the products (the one before
+    writes x * weight and partial sums of squares, the one after applies the rows' factors);
+    steps of many tokens run the norm's own kernel.  Both give the plain implementation's logits,
+    also where a small step follows a large one and where a layer is the last."""
+    cfg, w = P.read_model(models["B"])
+    toks = tiny.random_tokens(cfg["vocab_size"], 120, 5)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:90], "want": [0, 89]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[90:118], "want": [0, 27]}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": toks[118:], "want": [0, 1]}], "end": ["a"]}]
+    ref = P.forward(cfg, w, toks)
+    calls = {}
+    for fold in (True, False):
+        kernels = ReferenceKernels(fold=fold)
+        count = [0]
+        inner = kernels.linear_residual_norm
+
+        def spy(*a, _inner=inner, _count=count, **kw):
+            _count[0] += 1
+            return _inner(*a, **kw)
+        kernels.linear_residual_norm = spy
+        opts = EngineOptions(dtype="float32", device="cpu", page_size=tiny.TINY["B"]["page_size"], num_pages=40,
+                             max_num_seqs=4, max_num_batched_tokens=128)
+        eng = Engine.from_model_dir(models["B"], opts, kernels=kernels)
+        out = tiny.collect(steps, tiny.run_inprocess(eng.runner, steps), cfg["vocab_size"])
+        rows = [0, 89, 90, 117, 118, 119]
+        assert (out["a"] - ref[rows]).abs().max() < 2e-5, fold
+        calls[fold] = count[0]
+    layers = cfg["num_hidden_layers"]
+    assert calls[False] == 0
+    assert calls[True] == 2 * (2 * layers - 1)      # two small steps; every norm but the first of a step and the final one
+
+
 def test_greedy_generation_equals_the_plain_implementation(models):
     cfg, w = P.read_model(models["A"])
     eng = engine(models["A"], "A")

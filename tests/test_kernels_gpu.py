@@ -270,6 +270,46 @@ def test_linear_tcgen05(K, od, n, o, k, epilogue, shape):
                                atol=2e-3 if od == torch.bfloat16 else 1e-4)
 
 
+@pytest.mark.parametrize("n", [1, 8, 9, 33, 64])
+@pytest.mark.parametrize("hidden,inner,width2", [(72, 136, 40), (1000, 2048, 333), (1024, 3072, 4096)])
+@pytest.mark.parametrize("epilogue", ["none", "silu_gate"])
+@pytest.mark.parametrize("gdt", [torch.bfloat16, torch.float32])
+def test_linear_with_a_folded_norm(K, n, hidden, inner, width2, epilogue, gdt):
+    """x += a w1^T, RMSNorm, then a second product, with the norm done by the two products: the
+    first writes x * g and partial sums of squares, the second multiplies its rows by the factor.
+    Against the three steps done one after the other in float64."""
+    a = rnd((n, inner), torch.bfloat16, 1)
+    w1 = rnd((hidden, inner), torch.bfloat16, 2, scale=inner ** -0.5)
+    x = rnd((n, hidden), torch.float32, 3)
+    g = (1 + rnd((hidden,), torch.float32, 4, scale=0.1)).to(gdt)
+    w2 = rnd((2 * width2 if epilogue == "silu_gate" else width2, hidden), torch.bfloat16, 5, scale=hidden ** -0.5)
+    eps = 1e-5
+    x_ref = x.double() + a.double() @ w1.double().t()
+    r = torch.rsqrt((x_ref ** 2).mean(dim=1, keepdim=True) + eps)
+    xg = (x_ref * g.double()).to(torch.bfloat16)           # what the first product hands over
+    ref = torch.empty((n, width2), dtype=torch.float64)
+    REF.linear((xg.double() * r).to(torch.float64), w2, ref, epilogue)
+    assert K.can_fold_norm(n, torch.bfloat16, w1.cuda()) and K.can_fold_norm(n, torch.bfloat16, w2.cuda())
+    parts = K.fold_parts(hidden)
+    assert parts == -(-hidden // 16)
+    xd = x.cuda()
+    vals = torch.full((n, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    partials = torch.full((parts, n), float("nan"), dtype=torch.float32, device="cuda")
+    K.linear_residual_norm(a.cuda(), w1.cuda(), xd, g.cuda(), vals, partials)
+    torch.testing.assert_close(xd.cpu().double(), x_ref, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(partials.sum(dim=0).cpu().double(), (x_ref ** 2).sum(dim=1), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(vals.cpu().float(), xg.float(), rtol=1e-2, atol=1e-3)
+    for od in (torch.bfloat16, torch.float32):
+        out = torch.full((n, width2), float("nan"), dtype=od, device="cuda")
+        K.linear(vals, w2.cuda(), out, epilogue, row_scale=(partials, parts, eps, hidden))
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2 if od == torch.bfloat16 else 4e-3,
+                                   atol=4e-3 if od == torch.bfloat16 else 2e-3)
+    with pytest.raises(Exception):                          # many rows: no folded norm
+        big = torch.zeros((200, hidden), dtype=torch.bfloat16, device="cuda")
+        K.linear(big, w2.cuda(), torch.empty((200, width2), dtype=torch.bfloat16, device="cuda"), epilogue,
+                 row_scale=(torch.zeros((parts, 200), device="cuda"), parts, eps, hidden))
+
+
 @pytest.mark.parametrize("od", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("n,o,k", [(1, 72, 72), (8, 4096, 1024), (3, 1000, 3072), (16, 333, 136), (17, 64, 1024),
                                    (64, 1024, 2048), (33, 200, 1000), (1, 151936, 1024), (9, 17, 8)])
