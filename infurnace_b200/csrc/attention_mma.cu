@@ -498,14 +498,19 @@ attn_small_q_ws_kernel(const __grid_constant__ CUtensorMap kv_map, int total_row
   const uint32_t raw = smem_u32(smem_raw);
   bf16* KV = reinterpret_cast<bf16*>(smem_raw + (((raw + 1023u) & ~1023u) - raw));
   bf16* Qs = KV + SQ_STAGES * STAGE;                          // [16][DP]
-  ifb_pdl_wait();
-  ifb_pdl_trigger();
+  // (cu_q, seq_lens and the block tables were written at the start of the step, not by the kernel before this one:
+  // they may be read before waiting for it)
   const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = nq / nkv;
   const int q0 = cu_q[r], q_len = cu_q[r + 1] - q0, L = seq_lens[r];
   const int rows = q_len * G;
-  if (q_len <= 0 || rows > 16) return;
+  if (q_len <= 0 || rows > 16) {
+    // not this kernel's request.  Even so it waits for the kernel before it: a grid none of whose threads waited could
+    // end before its predecessor, and the kernel after this one, which waits for this one only, would start too early.
+    ifb_pdl_wait();
+    return;
+  }
   const int p_first = L - q_len;
   const int lo = window > 0 ? max(0, p_first - window + 1) : 0, hi = L - 1;
   const int total = hi + 1 - lo;
@@ -530,9 +535,17 @@ attn_small_q_ws_kernel(const __grid_constant__ CUtensorMap kv_map, int total_row
   for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
   bool ok = true;
   if (warp == 4) {
-    // ---- producer: tile t goes to stage t % S once the consumers have released that stage's previous tile
+    // ---- producer: tile t goes to stage t % S once the consumers have released that stage's previous tile.
+    // The kernel before this one wrote the keys and values of this step's tokens (positions >= p_first) and nothing
+    // else that is read here, so tiles of older keys are requested without waiting for it: the first stages fill
+    // while it still runs.
+    bool waited = false;
     for (int t = 0; t < n_tiles && ok; ++t) {
       const int stage = t % SQ_STAGES;
+      if (!waited && T0 + (t + 1) * BN > p_first) {
+        ifb_pdl_wait();
+        waited = true;
+      }
       if (t >= SQ_STAGES) ok = att_mbar_wait(&empty_bar[stage], ((t / SQ_STAGES) - 1) & 1, abort_flag, err, 3);
       if (!ok) break;
       tma_issue_tile(&kv_map, KV + stage * STAGE, &full_bar[stage], bt, T0 + t * BN, k_begin, k_end - 1, kvh, nkv, page_size,
@@ -540,6 +553,8 @@ attn_small_q_ws_kernel(const __grid_constant__ CUtensorMap kv_map, int total_row
     }
   } else {
     // ---- consumers: the query rows (row = token * G + head-in-group), then the tiles
+    ifb_pdl_wait();
+    ifb_pdl_trigger();
     for (int c = tid; c < 16 * KCH; c += 128) {
       const int row = c / KCH, ch = c % KCH;
       const bool valid = row < rows && n_tiles > 0;
