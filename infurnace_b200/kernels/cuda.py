@@ -8,6 +8,7 @@ a CUDA device or without the compiled library the constructor raises
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -82,6 +83,8 @@ class CudaKernels:
         self._lin_partials = None
         self._lin_counters = None
         self.gemv_max_rows = 64        # up to here: the kernel without global partial sums
+        # up to here norms are folded into products (the kernels take 64 rows; beyond 32 the separate norm measured faster)
+        self.fold_max_rows = int(os.environ.get("INFURNACE_FOLD_MAX_ROWS", "32"))
         self.skinny_max_rows = 4096    # above this the plain kernel runs (until a large-tile kernel takes over)
         self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
         self._dev_err = None           # device int: non-zero after a bounded barrier wait in a kernel gave up
@@ -206,7 +209,7 @@ class CudaKernels:
         """Whether a product of ``n`` rows of ``dtype`` against ``w`` runs on the kernel that can
         take or make a folded norm."""
         return (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
-                and 0 < n <= self.gemv_max_rows)
+                and 0 < n <= min(self.gemv_max_rows, self.fold_max_rows))
 
     def fold_parts(self, out_features):
         """Partial sums per row that :meth:`linear_residual_norm` writes."""

@@ -274,10 +274,12 @@ def test_linear_tcgen05(K, od, n, o, k, epilogue, shape):
 @pytest.mark.parametrize("hidden,inner,width2", [(72, 136, 40), (1000, 2048, 333), (1024, 3072, 4096)])
 @pytest.mark.parametrize("epilogue", ["none", "silu_gate"])
 @pytest.mark.parametrize("gdt", [torch.bfloat16, torch.float32])
-def test_linear_with_a_folded_norm(K, n, hidden, inner, width2, epilogue, gdt):
+def test_linear_with_a_folded_norm(K, n, hidden, inner, width2, epilogue, gdt, monkeypatch):
     """x += a w1^T, RMSNorm, then a second product, with the norm done by the two products: the
     first writes x * g and partial sums of squares, the second multiplies its rows by the factor.
-    Against the three steps done one after the other in float64."""
+    Against the three steps done one after the other in float64.  (The engine folds up to
+    fold_max_rows rows; the kernels take as many as the few-rows product does.)"""
+    monkeypatch.setattr(K, "fold_max_rows", 64)
     a = rnd((n, inner), torch.bfloat16, 1)
     w1 = rnd((hidden, inner), torch.bfloat16, 2, scale=inner ** -0.5)
     x = rnd((n, hidden), torch.float32, 3)
