@@ -290,20 +290,24 @@ class ModelRunner:
         recording.  A graph is dropped when a buffer it points at has moved."""
         greedy = sample and all(t == 0.0 for t in temperatures)
         build = dict(temperatures=temperatures, uniforms=uniforms) if sample else {}
-        if not self.use_graphs:
-            ctx = self._build_context(entries, **build)
-            self._apply_feed(ctx, feed)
-            return self._forward(ctx, sample, greedy)
+        # The padding and the length bucket are the same whether graphs are used or not, so that a step launches
+        # the same kernels with the same parameters either way (the split of a context over CTAs follows the bucket).
         longest = max(self.cache.num_computed(e.request_id) + len(e.tokens) for e in entries)
         seq_bucket = 256
         while seq_bucket < longest:
             seq_bucket *= 2
         decode_only = sample and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        r_bucket = 0
         if decode_only:
             r_bucket = 1
             while r_bucket < len(entries):
                 r_bucket *= 2
             r_bucket = min(r_bucket, self.max_requests)
+        if not self.use_graphs:
+            ctx = self._build_context(entries, pad_to=r_bucket, seq_bucket=seq_bucket, **build)
+            self._apply_feed(ctx, feed)
+            return self._forward(ctx, sample, greedy)
+        if decode_only:
             key = ("decode", r_bucket, seq_bucket, greedy)
             ctx = self._build_context(entries, pad_to=r_bucket, seq_bucket=seq_bucket, **build)
         else:

@@ -85,7 +85,8 @@ def fold_residual_norm(kernels, ctx, tag, a, w, fold, act_dtype):
         return None
     parts = kernels.fold_parts(o)
     out = ctx.buffer("folded_" + tag, (n, o), act_dtype)
-    partials = ctx.buffer("folded_partials_" + tag, (parts, n), __import__("torch").float32)
+    # one flat buffer whatever the number of rows, so that its address stays the same from step to step
+    partials = ctx.buffer("folded_partials_" + tag, (parts * n,), __import__("torch").float32).view(parts, n)
     kernels.linear_residual_norm(a, w, x, norm.weight, out, partials)
     return Folded(out, (partials, parts, float(norm.spec.eps), o))
 
