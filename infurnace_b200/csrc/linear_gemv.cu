@@ -195,7 +195,10 @@ static int gv_by_n(int nb, const void* x, const void* w, void* out, int n, int o
 template <int EPI, typename TO>
 static int gv_by_k(int nb, const void* x, const void* w, void* out, int n, int o, int k, const GvRowScale& rs,
                    const GvResidual& res, cudaStream_t s) {
-  // 128 of k per warp and step: 8 warps cover k up to 1024 in one step, 16 warps up to 2048
+  // 128 of k per warp and step: 8 warps cover k up to 1024 in one step, 16 warps up to 2048, 24 warps up to 3072 (a second
+  // step would request its weights only after the first step's products)
+  if (k > 2048 && nb == 1) return gv_launch<1, EPI, 24, TO>(x, w, out, n, o, k, rs, res, s);
+  if (k > 2048 && nb == 2) return gv_launch<2, EPI, 24, TO>(x, w, out, n, o, k, rs, res, s);
   return k > 1024 ? gv_by_n<EPI, 16, TO>(nb, x, w, out, n, o, k, rs, res, s) : gv_by_n<EPI, 8, TO>(nb, x, w, out, n, o, k, rs, res, s);
 }
 
