@@ -243,7 +243,10 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   const uint32_t tmem = tmem_slot;
 
   if (warp == 0) {
-    // ---------------- producer
+    // ---------------- producer.  Its wait orders the whole CTA behind the kernel before this one (which wrote the
+    // queries and this step's keys and values): the other warps act only on what its loads bring.
+    ifb_pdl_wait();
+    ifb_pdl_trigger();
     if (lane == 0) {
       tc_mbar_expect_tx(&bars.q_full, (n_x[1] > 0 ? 2 : 1) * TILE_BYTES);
 #pragma unroll
@@ -540,7 +543,6 @@ IFB_EXPORT int ifb_attention_tc(const void* qkv, int row_stride, const void* pag
   }
   const int tpc = 2 * (ROWS / G);                            // tokens per CTA: two query tiles
   dim3 grid((max_q_len + tpc - 1) / tpc, nkv, n_req);
-  attn_tile_tc_kernel<<<grid, TC_THREADS, SMEM_BYTES, stream>>>(q_map, kv_map, (int)rows, err, block_tables, bt_stride, cu_q, seq_lens,
-                                                                (bf16*)out, nq, nkv, page_size, scale * 1.4426950408889634f, window);
-  return ifb_launch_status();
+  return ifb_launch(attn_tile_tc_kernel, grid, dim3(TC_THREADS), (size_t)SMEM_BYTES, stream, q_map, kv_map, (int)rows, err, block_tables,
+                    bt_stride, cu_q, seq_lens, (bf16*)out, nq, nkv, page_size, scale * 1.4426950408889634f, window);
 }

@@ -168,15 +168,35 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   if (threadIdx.x == 0) G_STAMP(1);
 
   if (warp == 0) {
-    for (int kb = 0; kb < kblocks; ++kb) {
+    // The first fill of the stages: the w tiles, which no kernel of the step writes, are requested before this kernel
+    // waits for its predecessor in the stream; the x tiles after.  (The other warps act only on what these loads
+    // bring, so the wait of this warp orders the whole CTA behind the predecessor.)
+    const int first = min(kblocks, Cfg::STAGES);
+    if (elect_one()) {
+      for (int kb = 0; kb < first; ++kb) {
+        unsigned char* stage = smem + kb * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full[kb], Cfg::STAGE_BYTES);
+        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[kb], kb * G_BK, n0);               // FO rows of w
+        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[kb], kb * G_BK, o_out + n0);
+      }
+    }
+    __syncwarp();
+    ifb_pdl_wait();
+    ifb_pdl_trigger();
+    if (elect_one()) {
+      for (int kb = 0; kb < first; ++kb)
+        tma_load_2d(smem + kb * Cfg::STAGE_BYTES, &tmap_x, &full[kb], kb * G_BK, m0);       // MH * 128 rows of x
+    }
+    __syncwarp();
+    for (int kb = first; kb < kblocks; ++kb) {
       const int s = kb % Cfg::STAGES;
       const uint32_t ph = (kb / Cfg::STAGES) & 1;
       if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, err, 1)) break;
       if (elect_one()) {
         unsigned char* stage = smem + s * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-        tma_load_2d(stage, &tmap_x, &full[s], kb * G_BK, m0);                               // MH * 128 rows of x
-        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[s], kb * G_BK, n0);                // FO rows of w
+        tma_load_2d(stage, &tmap_x, &full[s], kb * G_BK, m0);
+        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[s], kb * G_BK, n0);
         if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[s], kb * G_BK, o_out + n0);
       }
       __syncwarp();
@@ -332,8 +352,7 @@ static int tc_launch_cfg(const void* x, const void* w, void* out, int n, int o, 
   }
   dim3 grid((o + Cfg::FO - 1) / Cfg::FO, (n + Cfg::MH * G_BM - 1) / (Cfg::MH * G_BM));
   if (grid.y > 65535) return IFB_ERR_SIZE;
-  linear_tcgen05_kernel<Cfg, TO><<<grid, G_THREADS, Cfg::SMEM_BYTES, s>>>(mx, mw, (TO*)out, n, o, k, err);
-  return ifb_launch_status();
+  return ifb_launch(linear_tcgen05_kernel<Cfg, TO>, grid, dim3(G_THREADS), (size_t)Cfg::SMEM_BYTES, s, mx, mw, (TO*)out, n, o, k, err);
 }
 
 // The shape of the tiles: a wave of wide tiles does four 128 x 128 products per SM in little more time than a wave of
