@@ -150,6 +150,11 @@ __device__ __forceinline__ float tc_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float tc_max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 __device__ __forceinline__ uint32_t tc_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -384,7 +389,8 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mxc[(c << 1) | (i & 1)] = fmaxf(mxc[(c << 1) | (i & 1)], __uint_as_float(v[c][i]));
+          for (int i = 0; i < 32; i += 2)                        // the three-input maximum: half the instructions
+            mxc[(c << 1) | ((i >> 1) & 1)] = tc_max3(mxc[(c << 1) | ((i >> 1) & 1)], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
       } else {
 #pragma unroll
         for (int c = 0; c < 2; ++c)
