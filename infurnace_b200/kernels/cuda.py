@@ -85,6 +85,7 @@ class CudaKernels:
         self.gemv_max_rows = 64        # up to here: the kernel without global partial sums
         # up to here norms are folded into products (the kernels take 64 rows; beyond 32 the separate norm measured faster)
         self.fold_max_rows = int(os.environ.get("INFURNACE_FOLD_MAX_ROWS", "32"))
+        self.split_min_keys = int(os.environ.get("INFURNACE_SPLIT_MIN_KEYS", "256"))   # fewest keys a split of a context gets
         self.skinny_max_rows = 4096    # above this the plain kernel runs (until a large-tile kernel takes over)
         self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
         self._dev_err = None           # device int: non-zero after a bounded barrier wait in a kernel gave up
@@ -367,10 +368,11 @@ class CudaKernels:
     def attention_splits(self, num_requests, num_kv_heads, max_seq_len, window=0):
         """How many CTAs share one (request, key/value head) of the small-q kernel: as many as
         keep the whole grid resident at once (two CTAs fit on an SM), so that no second wave
-        runs, and no fewer than 128 keys (two tiles) per split."""
+        runs, and no fewer than ``split_min_keys`` keys per split (256, four tiles: with 128 a lone
+        request's 32 partial results cost more to merge than the shorter splits saved)."""
         reach = min(max_seq_len, window + 16) if window else max_seq_len
         fit = (2 * self.sm_count) // max(1, num_requests * num_kv_heads)
-        return max(1, min(fit, -(-reach // 128), 32))
+        return max(1, min(fit, -(-reach // self.split_min_keys), 32))
 
     def attention_scratch(self, floats):
         if self._attn_scratch is None or self._attn_scratch.numel() < floats:
