@@ -51,10 +51,10 @@ def read_peaks():
     try:
         with open(path) as f:
             d = json.load(f)
-        hbm = float(d.get("hbm_gbs", hbm))
-        tf = float(d.get("bf16_tflops", tf))
-        src = "measured"
-    except (OSError, ValueError):
+        got_hbm, got_tf = d.get("hbm_gbs"), d.get("bf16_tflops")
+        if isinstance(got_hbm, (int, float)) and got_hbm > 0 and isinstance(got_tf, (int, float)) and got_tf > 0:
+            hbm, tf, src = float(got_hbm), float(got_tf), "measured"
+    except (OSError, ValueError, TypeError, AttributeError):
         pass
     return hbm, tf, src
 
