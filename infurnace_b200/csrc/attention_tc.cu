@@ -1,20 +1,24 @@
 // Attention for prompts and long portions on the fifth-generation tensor cores, head size 128.
 //
-// A CTA takes 128 score rows of one key/value head: 128/G query tokens times the G query heads of the
-// group (row = token * G + head-in-group), and walks the request's keys in tiles of 128.  Per tile:
-//   S = Q K^T     tcgen05.mma, Q and K in shared memory (TMA, 128-byte swizzle), S in tensor memory;
-//   softmax       four warps, one thread per row: the row of S is read from tensor memory, masked,
-//                 exponentiated against the running maximum (float32), summed, and written back to
-//                 tensor memory as bfloat16 P; the running output is rescaled in tensor memory only
-//                 when a maximum grew by more than 2^8 (the kept maximum may lag by that much, which
-//                 float32 sums and bfloat16 P hold without loss);
-//   O += P V      tcgen05.mma with P as the A operand in tensor memory and V from shared memory as an
-//                 MN-major B operand (V is stored [key][dim], the dim running fastest).
-// Warp 0 issues the TMA loads (the query tile through a three-dimensional tensor map over the fused
-// qkv rows, key/value tiles page by page as in attention_mma.cu), one thread of warp 1 issues the MMAs,
-// warps 2-5 do the softmax and the final division and store.  K and V have one buffer each with barriers
-// of their own: the next K tile is fetched while this tile's softmax runs, the next V tile while the
-// next scores are formed.  Two CTAs share an SM, so one's softmax runs beside the other's MMAs.
+// A CTA takes two query tiles of 128 score rows of one key/value head: a tile is 128/G query tokens times the G
+// query heads of the group (row = token * G + head-in-group).  Both tiles walk the same keys, loaded once, in
+// tiles of 128 (two stages each for K and V) and worked on in halves of 64.  Per query tile and half u:
+//   S[u & 1] = Q K^T  tcgen05.mma, Q and K in shared memory (TMA, 128-byte swizzle), the scores in one of the
+//                     tile's two score buffers in tensor memory, so that S(u+1) is formed while the softmax of
+//                     S(u) runs;
+//   softmax           four warps per query tile, one thread per row: the row's 64 scores are read from tensor
+//                     memory into registers, masked, exponentiated against the running maximum (float32), summed,
+//                     and written back over the scores as bfloat16 P; the running output is rescaled in tensor
+//                     memory only when a maximum grew by more than 2^8 (the kept maximum may lag by that much,
+//                     which float32 sums and bfloat16 P hold without loss);
+//   O += P V          tcgen05.mma with P as the A operand in tensor memory and V from shared memory as an
+//                     MN-major B operand (V is stored [key][dim], the dim running fastest).
+// Warp 0 issues the TMA loads (the query tiles through a three-dimensional tensor map over the fused qkv rows,
+// key/value tiles page by page as in attention_mma.cu) after waiting for the kernel before this one; warps 1 and
+// 2 issue the MMAs of query tile 0 and 1 (all lanes wait on the barriers, one lane elected by elect.sync issues:
+// descriptors then live in uniform registers, which is worth 40 cycles per MMA); warp 3 idles; warps 4-7 and 8-11
+// do the softmax and the final division and store of query tile 0 and 1.  Tensor memory: per query tile two score
+// buffers of 64 columns and 128 columns of output, 512 columns in all, so one CTA per SM.
 //
 // Requests are routed as in attention_mma.cu: this kernel takes those with more than 16 score rows,
 // the small-q kernel there takes the others.  Waits on barriers are bounded (TC_SPIN_LIMIT polls, then
@@ -41,8 +45,8 @@ constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 constexpr int HALF_BYTES = 128 * 128;     // a [128 rows][64 columns] bf16 half tile in the 128-byte swizzle: 16 KB
 constexpr int TILE_BYTES = 2 * HALF_BYTES;
 constexpr int SMEM_BYTES = 6 * TILE_BYTES /* 2 Q, 2 K, 2 V */ + 1024 /* alignment */;   // 193 KB: one CTA per SM
-// tensor memory columns (32-bit), per query tile: S [0,128) with P (bfloat16 pairs) written over its first 64 once
-// the row has been read, O [128,256).  Two query tiles: all 512 columns of the SM.
+// tensor memory columns (32-bit), per query tile: two score buffers [0,64) and [64,128), P (bfloat16 pairs) written
+// over the first 32 columns of a buffer once its row has been read, O [128,256).  Two query tiles: all 512 columns.
 constexpr int COL_S = 0, COL_O = 128, COLS_PER_TILE = 256, TMEM_COLS = 512;
 constexpr int NO_ROW = -1000000000;
 
