@@ -757,14 +757,9 @@ static int att_launch(const CUtensorMap& map, int total_rows, int* err, const vo
                       const int* block_tables, int bt_stride, const int* cu_q, const int* seq_lens, void* out, float* scratch,
                       int* counters, int n_tokens, int n_req, int nq, int nkv, int page_size, float scale_log2, int window,
                       int max_q_len, int num_splits, int run_small, int run_tiles, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = TMA ? cudaFuncSetAttribute(attn_small_q_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_q_smem(true))
-                        : cudaFuncSetAttribute(attn_small_q_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_q_smem(false));
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_tile_kernel<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem(TMA));
-    if (e != cudaSuccess) return -(int)e;
-    configured = true;
-  }
+  if (TMA) IFB_ALLOW_SMEM(attn_small_q_ws_kernel, small_q_smem(true));
+  else IFB_ALLOW_SMEM(attn_small_q_kernel<false>, small_q_smem(false));
+  IFB_ALLOW_SMEM(attn_tile_kernel<TMA>, tile_smem(TMA));
   const int G = nq / nkv;
   if (run_small) {
     float* part_o = scratch;

@@ -50,13 +50,6 @@ constexpr int SMEM_BYTES = 6 * TILE_BYTES /* 2 Q, 2 K, 2 V */ + 1024 /* alignmen
 constexpr int COL_S = 0, COL_O = 128, COLS_PER_TILE = 256, TMEM_COLS = 512;
 constexpr int NO_ROW = -1000000000;
 
-#ifdef TC_TRACE
-// Timestamps of the phases of one CTA (the one with the longest key range of head 0), for tuning builds only.
-__device__ long long tc_trace_buf[4][64][8];
-#define TC_STAMP(who, j, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64) tc_trace_buf[who][j][k] = clock64(); } while (0)
-#else
-#define TC_STAMP(who, j, k) do {} while (0)
-#endif
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void tc_mbar_init(uint64_t* bar, int count) {
@@ -204,10 +197,12 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   const int kvh = blockIdx.y, r = blockIdx.z;
   const int G = nq / nkv;
   const int q0 = cu_q[r], q_len = cu_q[r + 1] - q0, L = seq_lens[r];
-  if (q_len * G <= 16) return;                               // the small-q kernel's request
+  // every exit path waits for the predecessor: a grid none of whose threads waited could end before the kernel that
+  // stores this step's keys, and its own successor, which waits for this grid alone, would then start too early
+  if (q_len * G <= 16) { ifb_pdl_wait(); return; }           // the small-q kernel's request
   const int tpt = ROWS / G;                                  // tokens per query tile; a CTA takes two tiles
   const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * 2 * tpt;   // longest key ranges first
-  if (t0 >= q_len) return;
+  if (t0 >= q_len) { ifb_pdl_wait(); return; }
   const int t1 = min(q_len, t0 + 2 * tpt);
   const int p_first = L - q_len;
   const int lo = window > 0 ? max(0, p_first + t0 - window + 1) : 0, hi = p_first + t1 - 1;
@@ -280,7 +275,6 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
               ok = tc_mbar_wait(kv ? &bars.v_empty[x][st] : &bars.k_empty[x][st], ((j >> 1) - 1) & 1, abort_flag, err, 11);
         }
         if (!ok) break;
-        if (lane == 0) TC_STAMP(0, j, kv);
         if (lane == 0) tc_mbar_expect_tx(full, TILE_BYTES);
         __syncwarp();
         if (lane < n_ops) {
@@ -330,12 +324,10 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     if (ok && n_mine > 1) issue_qk(1);
     for (int u = 0; u < n_mine && ok; ++u) {
       const int st = (u >> 1) & 1;
-      if (x == 0) TC_STAMP(1, u, 0);
       if (!(u & 1)) ok = tc_mbar_wait(&bars.v_full[st], (u >> 2) & 1, abort_flag, err, 18);
       ok = ok && tc_mbar_wait(&bars.p_ready[x][u & 1], (u >> 1) & 1, abort_flag, err, 14);
       if (!ok) break;
       tc_fence_after();
-      if (x == 0) TC_STAMP(1, u, 1);
       // O += P(u) V: 4 steps of 16 keys; P at 8 columns (16 bfloat16) per step, V 2048 bytes (16 key rows) per step
       if (tc_elect_one()) {
         const uint64_t vd = desc_mn_major(v_addr + st * TILE_BYTES + (u & 1) * (SUB * 128));
@@ -346,13 +338,11 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         if ((u & 1) || u == n_mine - 1) tc_commit(&bars.v_empty[x][st]);
       }
       __syncwarp();
-      if (x == 0) TC_STAMP(1, u, 2);
       if (u + 2 < n_mine) {
         wait_k(u + 2);
         if (!ok) break;
         issue_qk(u + 2);
       }
-      if (x == 0) TC_STAMP(1, u, 3);
     }
   } else if (warp >= 4) {
     // ---------------- softmax: warps 4-7 take query tile 0, warps 8-11 query tile 1; one thread per row
@@ -367,7 +357,6 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16) + x * COLS_PER_TILE;
     uint64_t* o_done = &bars.o_done[x];
     const int n_mine = x ? n_x[1] : n_x[0];
-    const bool stamp = (threadIdx.x & 127) == 64;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int u = 0; u < n_mine && ok; ++u) {
@@ -375,7 +364,6 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       ok = __all_sync(0xffffffffu, tc_mbar_wait(&bars.s_full[x][h], (u >> 1) & 1, abort_flag, err, 15)) != 0;    // warp-uniform
       if (!ok) break;
       tc_fence_after();
-      if (stamp) TC_STAMP(2 + x, u, 0);
       const int key0 = T0 + u * SUB;
       const uint32_t s_addr = lane_addr + COL_S + h * SUB;
       // a half every key of which every row of the query tile sees needs no masking (rows past the request's tokens
@@ -386,7 +374,6 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #pragma unroll
       for (int c = 0; c < 2; ++c) tc_ld32(s_addr + c * 32, v[c]);
       tc_wait_ld();
-      if (stamp) TC_STAMP(2 + x, u, 1);
       // the row's maximum over the visible keys, four chains
       float mxc[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (interior) {
@@ -417,7 +404,6 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         m_used = m_new;
       }
       const float ref = m_used == -INFINITY ? 0.f : m_used;
-      if (stamp) TC_STAMP(2 + x, u, 2);
       if (u > 0 && any_grow) {
         // O is rescaled between the previous half's P V, which must have landed, and this half's, which waits for P
         ok = __all_sync(0xffffffffu, tc_mbar_wait(o_done, (u - 1) & 1, abort_flag, err, 16)) != 0;
@@ -463,11 +449,9 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         tc_st16(s_addr + c * 16, pk);
       }
       l += (lc[0] + lc[1]) + (lc[2] + lc[3]);
-      if (stamp) TC_STAMP(2 + x, u, 3);
       tc_wait_st();
       tc_fence_before();
       tc_mbar_arrive(&bars.p_ready[x][h]);
-      if (stamp) TC_STAMP(2 + x, u, 4);
     }
     if (ok && n_mine > 0) {
       ok = __all_sync(0xffffffffu, tc_mbar_wait(o_done, (n_mine - 1) & 1, abort_flag, err, 17)) != 0;
@@ -509,11 +493,6 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   }
 }
 
-#ifdef TC_TRACE
-IFB_EXPORT int ifb_attention_tc_trace(long long* host) {
-  return cudaMemcpyFromSymbol(host, tc_trace_buf, sizeof(tc_trace_buf)) == cudaSuccess ? IFB_OK : IFB_ERR_ARG;
-}
-#endif
 
 // ---------------------------------------------------------------------------------------------------
 // qkv [n_tokens, row_stride] bfloat16 (the q heads are the first nq * 128 columns), pages [num_pages, 2, nkv, page_size, 128],
@@ -545,12 +524,7 @@ IFB_EXPORT int ifb_attention_tc(const void* qkv, int row_stride, const void* pag
     const unsigned box[2] = {64, (unsigned)page_size};
     if (ifb_tensor_map_bf16(&kv_map, pages, 2, dims, strides, box)) return IFB_ERR_ARG;
   }
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_tile_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return -(int)e;
-    configured = true;
-  }
+  IFB_ALLOW_SMEM(attn_tile_tc_kernel, SMEM_BYTES);
   const int tpc = 2 * (ROWS / G);                            // tokens per CTA: two query tiles
   dim3 grid((max_q_len + tpc - 1) / tpc, nkv, n_req);
   return ifb_launch(attn_tile_tc_kernel, grid, dim3(TC_THREADS), (size_t)SMEM_BYTES, stream, q_map, kv_map, (int)rows, err, block_tables,

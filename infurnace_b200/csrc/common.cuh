@@ -16,6 +16,10 @@
 #define IFB_ERR_ALIGN 3      // a pointer or a row length breaks the kernel's alignment rule
 #define IFB_ERR_ARG 4        // an argument contradicts another
 
+// Codes that kernels record in the device error word (an int the caller passes and reads back later).  Codes below
+// 900 are given by the kernels that wait on barriers: which wait gave up.
+#define IFB_DEV_ERR_TOKEN_ID 900   // a token id outside the vocabulary reached the embedding
+
 #define IFB_EXPORT extern "C" __attribute__((visibility("default")))
 
 static inline int ifb_launch_status() {
@@ -42,6 +46,21 @@ static inline bool ifb_pdl_enabled() {
   if (on < 0) { const char* e = getenv("IFB_PDL"); on = (e && e[0] == '0') ? 0 : 1; }
   return on != 0;
 }
+
+// The largest dynamic shared memory a kernel may be launched with is an attribute of (kernel, device), so what has been
+// set is remembered per device, at the call site.  On failure the enclosing function returns the negated CUDA error.
+#define IFB_MAX_DEVICES 64
+#define IFB_ALLOW_SMEM(kernel, bytes)                                                                                   \
+  do {                                                                                                                  \
+    static size_t ifb_allowed_[IFB_MAX_DEVICES] = {};                                                                   \
+    int ifb_dev_ = 0;                                                                                                   \
+    if (cudaGetDevice(&ifb_dev_) != cudaSuccess || ifb_dev_ < 0 || ifb_dev_ >= IFB_MAX_DEVICES) return IFB_ERR_ARG;     \
+    if ((size_t)(bytes) > 48 * 1024 && (size_t)(bytes) > ifb_allowed_[ifb_dev_]) {                                      \
+      cudaError_t ifb_e_ = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes));     \
+      if (ifb_e_ != cudaSuccess) return -(int)ifb_e_;                                                                   \
+      ifb_allowed_[ifb_dev_] = (size_t)(bytes);                                                                         \
+    }                                                                                                                   \
+  } while (0)
 
 template <typename... KArgs, typename... Args>
 static inline int ifb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {

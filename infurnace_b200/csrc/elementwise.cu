@@ -6,22 +6,31 @@
 
 // ------------------------------------------------------------------------------------------
 // embed: out[n, :] = float(table[ids[n], :])
+// An id outside [0, vocab) (ids may come straight from the sampling kernel of the step before, unseen by the
+// host) reads no memory: the row is written as zeros and IFB_DEV_ERR_TOKEN_ID is recorded in *err (if given).
 // ------------------------------------------------------------------------------------------
 __global__ void embed_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ ids,
-                             float* __restrict__ out, int hidden) {
+                             float* __restrict__ out, int hidden, int vocab, int* __restrict__ err) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int n = blockIdx.x;
-  const size_t row = (size_t)ids[n] * hidden;
+  const int id = ids[n];
+  if (id < 0 || id >= vocab) {
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[(size_t)n * hidden + h] = 0.f;
+    if (err && threadIdx.x == 0) atomicCAS(err, 0, IFB_DEV_ERR_TOKEN_ID);
+    return;
+  }
+  const size_t row = (size_t)id * hidden;
   for (int h = threadIdx.x; h < hidden; h += blockDim.x)
     out[(size_t)n * hidden + h] = load_as_f32(table, table_dtype, row + h);
 }
 
-IFB_EXPORT int ifb_embed(const void* table, int table_dtype, const int* ids, float* out, int n, int hidden,
-                         cudaStream_t stream) {
+IFB_EXPORT int ifb_embed(const void* table, int table_dtype, const int* ids, float* out, int n, int hidden, int vocab,
+                         int* err, cudaStream_t stream) {
   if (n <= 0) return IFB_OK;
   if (table_dtype != IFB_F32 && table_dtype != IFB_BF16) return IFB_ERR_DTYPE;
-  return ifb_launch(embed_kernel, dim3(n), dim3(256), 0, stream, table, table_dtype, ids, out, hidden);
+  if (vocab < 1) return IFB_ERR_SIZE;
+  return ifb_launch(embed_kernel, dim3(n), dim3(256), 0, stream, table, table_dtype, ids, out, hidden, vocab, err);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -133,12 +142,7 @@ IFB_EXPORT int ifb_rmsnorm(float* x, const float* delta, int num_splits, long lo
   }
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return IFB_ERR_SIZE;
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return -(int)e;
-    configured = smem;
-  }
+  IFB_ALLOW_SMEM(rmsnorm_kernel, smem);
   const int threads = hidden >= 2048 ? 512 : 256;
   return ifb_launch(rmsnorm_kernel, dim3(num_out_rows), dim3(threads), smem, stream, x, delta, delta ? num_splits : 0,
                     (size_t)split_stride, w, w_dtype, eps, out, out_dtype, rows, hidden);
@@ -402,7 +406,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, const
   const int begin = min(vocab, tid * chunk), end = min(vocab, begin + chunk);
   // the largest value and its lowest index; the row is walked with consecutive threads on consecutive
   // elements (any partition gives the same answer, since ties go to the lower index)
-  float bv = -INFINITY; int bi = 0x7fffffff;
+  float bv = -INFINITY; int bi = 0;      // a row without any comparable value (all NaN) gives index 0, never an id outside the vocabulary
   if ((((uintptr_t)l) & 15) == 0) {      // 16-byte loads, four in flight per thread
     const int v4 = vocab >> 2;
     const float4* l4 = reinterpret_cast<const float4*>(l);
@@ -427,7 +431,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, const
   __syncthreads();
   if (tid < 32) {
     const int nw = (nthreads + 31) >> 5;
-    bv = tid < nw ? best_val[tid] : -INFINITY; bi = tid < nw ? best_idx[tid] : 0x7fffffff;
+    bv = tid < nw ? best_val[tid] : -INFINITY; bi = tid < nw ? best_idx[tid] : 0;
     for (int o = 16; o > 0; o >>= 1) {
       float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
@@ -457,7 +461,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, const
       pick = best_idx[0];
       for (int i = vocab - 1; i >= 0; --i) if (expf((l[i] - mx) * inv_t) > 0.f) { pick = i; break; }
     }
-    chosen = pick;
+    chosen = min(max(pick, 0), vocab - 1);
   }
   __syncthreads();
   if (tid == 0) out[row] = chosen;

@@ -170,12 +170,7 @@ template <int NB, int EPI, int WARPS, typename TO>
 static int gv_launch(const void* x, const void* w, void* out, int n, int o, int k, const GvRowScale& rs, const GvResidual& res,
                      cudaStream_t s) {
   const size_t smem = ((size_t)WARPS * (EPI == 1 ? 2 : 1) * NB * 8 * GV_ROWS + NB * 8) * sizeof(float);
-  static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(linear_gemv_kernel<NB, EPI, WARPS, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return -(int)e;
-    configured = true;
-  }
+  IFB_ALLOW_SMEM((linear_gemv_kernel<NB, EPI, WARPS, TO>), smem);
   dim3 grid((o + GV_ROWS - 1) / GV_ROWS, (n + NB * 8 - 1) / (NB * 8));
   return ifb_launch(linear_gemv_kernel<NB, EPI, WARPS, TO>, grid, dim3(WARPS * 32), smem, s, (const bf16*)x, (const bf16*)w,
                     (TO*)out, n, o, k, rs, res);

@@ -177,12 +177,7 @@ template <int NB, int EPI, typename TO>
 static int sk_launch(const void* x, const void* w, void* out, float* partials, int* counters, int n, int o, int k,
                      int splits, int kps, cudaStream_t s) {
   const size_t smem = (size_t)NB * 8 * (SK_KC + SK_XPAD) * sizeof(bf16);
-  static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NB, EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return -(int)e;
-    configured = true;
-  }
+  IFB_ALLOW_SMEM((linear_skinny_kernel<NB, EPI, TO>), smem);
   dim3 grid((o + SK_ROWS - 1) / SK_ROWS, splits, (n + NB * 8 - 1) / (NB * 8));
   return ifb_launch(linear_skinny_kernel<NB, EPI, TO>, grid, dim3(SK_THREADS), smem, s, (const bf16*)x, (const bf16*)w,
                     (TO*)out, partials, counters, n, o, k, splits, kps);

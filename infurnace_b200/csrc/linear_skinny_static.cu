@@ -9,7 +9,10 @@
 static __device__ __align__(256) float g_static_partials[IFB_STATIC_SCRATCH_FLOATS];
 static __device__ __align__(256) int g_static_counters[IFB_STATIC_SCRATCH_COUNTERS];
 
+#include <mutex>
+
 #define IFB_STATIC_MAX_DEVICES 64
+static std::mutex g_setup_lock;                 // first calls from several threads: one looks up, the others wait
 static float* g_partials_addr[IFB_STATIC_MAX_DEVICES];
 static int* g_counters_addr[IFB_STATIC_MAX_DEVICES];
 
@@ -34,18 +37,24 @@ IFB_EXPORT int ifb_linear_skinny_static(const void* x, const void* w, void* out,
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return -(int)e;
   if (dev < 0 || dev >= IFB_STATIC_MAX_DEVICES) return IFB_ERR_ARG;
-  if (!g_partials_addr[dev]) {            // set-up, once per device, with that device current
-    float* p = nullptr;
-    int* c = nullptr;
-    e = cudaGetSymbolAddress((void**)&p, g_static_partials);
-    if (e != cudaSuccess) return -(int)e;
-    e = cudaGetSymbolAddress((void**)&c, g_static_counters);
-    if (e != cudaSuccess) return -(int)e;
-    g_counters_addr[dev] = c;
-    g_partials_addr[dev] = p;
+  float* partials = nullptr;
+  int* counters = nullptr;
+  {
+    std::lock_guard<std::mutex> hold(g_setup_lock);
+    if (!g_partials_addr[dev] || !g_counters_addr[dev]) {      // set-up, once per device, with that device current
+      float* p = nullptr;
+      int* c = nullptr;
+      e = cudaGetSymbolAddress((void**)&p, g_static_partials);
+      if (e != cudaSuccess) return -(int)e;
+      e = cudaGetSymbolAddress((void**)&c, g_static_counters);
+      if (e != cudaSuccess) return -(int)e;
+      if (!p || !c) return IFB_ERR_ARG;
+      g_counters_addr[dev] = c;
+      g_partials_addr[dev] = p;
+    }
+    partials = g_partials_addr[dev];
+    counters = g_counters_addr[dev];
   }
-  float* partials = g_partials_addr[dev];
-  int* counters = g_counters_addr[dev];
   if (need_c > 0) {
     // the counters must start at zero; an earlier call that failed half-way may have left some raised
     e = cudaMemsetAsync(counters, 0, (size_t)need_c * sizeof(int), stream);

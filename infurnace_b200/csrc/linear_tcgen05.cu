@@ -127,13 +127,6 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-#ifdef G_TRACE
-// Timestamps of the phases of CTA (0, 0), for tuning builds only.
-__device__ long long g_trace_buf[16];
-#define G_STAMP(k) do { if (blockIdx.x == 0 && blockIdx.y == 0) g_trace_buf[k] = clock64(); } while (0)
-#else
-#define G_STAMP(k) do {} while (0)
-#endif
 
 template <typename Cfg, typename TO>
 __global__ void __launch_bounds__(G_THREADS)
@@ -151,7 +144,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;     // warp-uniform
   const int m0 = blockIdx.y * (MH * G_BM), n0 = blockIdx.x * FO;
   const int kblocks = (k_dim + G_BK - 1) / G_BK;
-  if (threadIdx.x == 0) G_STAMP(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -165,7 +157,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) G_STAMP(1);
 
   if (warp == 0) {
     // The first fill of the stages: the w tiles, which no kernel of the step writes, are requested before this kernel
@@ -209,9 +200,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       ok = mbar_wait(&full[s], ph, abort_flag, err, 2);
       if (!ok) break;
       tc_fence_after();
-      if (lane == 0 && kb == 0) G_STAMP(2);
-      if (lane == 0 && kb == 1) G_STAMP(3);
-      if (lane == 0 && kb == kblocks - 1) G_STAMP(4);
       if (elect_one()) {
         const uint32_t a_addr = g_smem_u32(smem + s * Cfg::STAGE_BYTES);
         const uint64_t a_desc = make_smem_desc(a_addr);
@@ -243,7 +231,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     const int c_lo = ((warp - 2) >> 2) * CW;                     // and its half of the tile's features
     if (mbar_wait(accum, 0, abort_flag, err, 3)) {
       tc_fence_after();
-      if (threadIdx.x == 64) G_STAMP(5);
       const bool vec = ((size_t)o_out * sizeof(TO)) % 16 == 0 && (((uintptr_t)out) & 15) == 0 && n0 + c_lo + CW <= o_out;
       unsigned char* buf = smem + (warp - 2) * (32 * PITCH);
 #pragma unroll 1
@@ -313,7 +300,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       }
     }
   }
-  if (threadIdx.x == 64) G_STAMP(6);
   if (*abort_flag) {                         // a wait gave up: let copies in flight land before the CTA goes away
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
@@ -322,11 +308,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, Cfg::TMEM_COLS); }
 }
 
-#ifdef G_TRACE
-IFB_EXPORT int ifb_linear_tcgen05_trace(long long* host) {
-  return cudaMemcpyFromSymbol(host, g_trace_buf, sizeof(g_trace_buf)) == cudaSuccess ? IFB_OK : IFB_ERR_ARG;
-}
-#endif
 
 // ---------------------------------------------------------------------------------------------------
 // A [rows, k] bfloat16 row-major matrix as a tensor map with boxes of 64 k x box_rows rows, 128-byte swizzle.
@@ -344,12 +325,7 @@ static int tc_launch_cfg(const void* x, const void* w, void* out, int n, int o, 
   if (st) return st;
   st = make_map(&mw, w, Cfg::EPI ? 2 * o : o, k, Cfg::EPI ? Cfg::NACC / 2 : Cfg::NACC);
   if (st) return st;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_kernel<Cfg, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return -(int)e;
-    configured = true;
-  }
+  IFB_ALLOW_SMEM((linear_tcgen05_kernel<Cfg, TO>), Cfg::SMEM_BYTES);
   dim3 grid((o + Cfg::FO - 1) / Cfg::FO, (n + Cfg::MH * G_BM - 1) / (Cfg::MH * G_BM));
   if (grid.y > 65535) return IFB_ERR_SIZE;
   return ifb_launch(linear_tcgen05_kernel<Cfg, TO>, grid, dim3(G_THREADS), (size_t)Cfg::SMEM_BYTES, s, mx, mw, (TO*)out, n, o, k, err);

@@ -8,7 +8,10 @@ function, and sampling happens on the device for all its rows at once.
 
 Failures are contained as in the reference (engine.py:125-132,195-197): an exception from
 the step function turns the requests of that step into FAILED ones, their pages and slots
-go back, and the engine goes on with the others.
+go back, and the engine goes on with the others.  A fault that a kernel contained and
+recorded on the device (a bounded wait that gave up, a token id outside the vocabulary) is
+read every 32 steps and before any request is reported finished; it fails every request
+that ran since the error word was last read clean.
 """
 from __future__ import annotations
 
@@ -18,7 +21,7 @@ import traceback
 from dataclasses import dataclass, field
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
-from ..errors import OutOfPages
+from ..errors import KernelError, OutOfPages
 from ..sampling import Sampler, uniform
 from ..tokenizer import StreamingDetokenizer, Tokenizer, check_stop_strings
 from .loading import EngineOptions, build_runner
@@ -63,6 +66,7 @@ class Engine:
         self._detoks: Dict[str, StreamingDetokenizer] = {}
         self._count = 0
         self._steps_since_check = 0
+        self._ran_since_check: set = set()             # requests with a step launched since the error word was read clean
         self._inflight: Optional[RawStep] = None       # a step launched ahead of the one being committed
         self.overlap_decode = True
 
@@ -154,6 +158,7 @@ class Engine:
             raw.sampled = [e.request_id for e in sampled]
             for e in plan.entries:                 # the tokens' keys and values are in the pages now
                 self.scheduler.advance(e)
+                self._ran_since_check.add(e.request_id)
             self._steps_since_check += 1
         except Exception as e:  # a failed step fails its requests, not the engine
             if not isinstance(e, OutOfPages):
@@ -165,16 +170,15 @@ class Engine:
         plan, sch = raw.plan, self.scheduler
         if raw.error is None and raw.handle is not None:
             raw.tokens = {rid: int(t) for rid, t in zip(raw.sampled, raw.handle.tolist())}
-            if self._steps_since_check >= 32:      # reading the kernels' error word costs a device round trip
-                self.check_device_errors()
         completed, failed = [], list(plan.failed)
         new_tokens: Dict[str, List[int]] = {}
         new_text: Dict[str, str] = {}
         metrics: Dict[str, RequestMetrics] = {}
+        finishing: List[Tuple[str, str]] = []
         n_prefill = n_decode = 0
         for e in plan.entries:
             req = sch.get_request(e.request_id)
-            if req.is_terminal():        # cancelled between the phases: its output is dropped
+            if req.is_terminal():        # cancelled or failed between the phases: its output is dropped
                 continue
             if raw.error is not None:
                 sch.fail(e.request_id, raw.error)
@@ -207,9 +211,18 @@ class Engine:
                     detok.truncate(keep)
                     new_text[e.request_id] = detok.text[before:]
             if reason is not None:
-                sch.finish(e.request_id, reason)
-                metrics[e.request_id] = req.metrics
-                completed.append(e.request_id)
+                finishing.append((e.request_id, reason))
+        # reading the kernels' error word costs a device round trip: every 32 steps, and before a request is
+        # reported finished (so that no request finishes on output that a kernel had marked invalid)
+        if raw.error is None and (finishing or self._steps_since_check >= 32):
+            failed.extend(self.contain_device_errors())
+        for rid, reason in finishing:
+            req = sch.get_request(rid)
+            if req.is_terminal():
+                continue
+            sch.finish(rid, reason)
+            metrics[rid] = req.metrics
+            completed.append(rid)
         return EngineStepResult(
             completed_requests=tuple(completed), new_tokens={k: tuple(v) for k, v in new_tokens.items()},
             new_text=new_text, metrics=metrics, failed_requests=tuple(failed),
@@ -261,12 +274,31 @@ class Engine:
         return StepPlan(entries=entries), rows
 
     def check_device_errors(self) -> None:
-        """Raise if a kernel recorded that a bounded wait on a barrier gave up since the last check
-        (done every 32 steps, and when ``generate`` ends)."""
+        """Raise if a kernel recorded a fault since the error word was last read (a bounded wait on a
+        barrier that gave up, a token id outside the vocabulary)."""
         self._steps_since_check = 0
         check = getattr(self.runner.rt.kernels, "check_device_errors", None)
         if check is not None:
             check()
+        self._ran_since_check.clear()
+
+    def contain_device_errors(self) -> List[str]:
+        """Read the kernels' error word; if it is set, every request that had a step launched since it
+        was last read clean FAILS (pages and state slot back, the error as its ``error``), as a runner
+        exception fails the requests of its step (src/infurnace/engine/engine.py:125-132).  Returns the
+        ids of the requests that failed.  A step launched ahead for them is dropped at its commit."""
+        try:
+            self.check_device_errors()
+            return []
+        except KernelError as err:
+            failed = []
+            for rid in sorted(self._ran_since_check):
+                req = self.scheduler.get_request(rid)
+                if not req.is_terminal():
+                    self.scheduler.fail(rid, f"KernelError: {err}")
+                    failed.append(rid)
+            self._ran_since_check.clear()
+            return failed
 
     # ------------------------------------------------------------------ conveniences
     def generate(self, prompts: Sequence[Sequence[int]], sampling_params=None) -> List[List[int]]:
@@ -287,7 +319,7 @@ class Engine:
             idle_steps = 0 if moved else idle_steps + 1
             if idle_steps > 100:
                 raise RuntimeError("the scheduler made no progress in 100 steps")
-        self.check_device_errors()
+        self.contain_device_errors()
         out = []
         for rid in ids:
             req = self.scheduler.get_request(rid)

@@ -134,10 +134,13 @@ class ModelRunner:
         self.max_model_len = max_model_len
         self.max_requests = cache.max_requests
         self.max_pages = -(-max_model_len // cache.page_size)
-        self.arena = _Arena(runtime.device, max_tokens)
+        # rows of the flat token axis that the staging regions and buffers hold: a decode-only step is padded to
+        # a power-of-two number of requests (at most max_requests), which may exceed the token budget
+        self._n_cap = max(max_tokens, self.max_requests)
+        self.arena = _Arena(runtime.device, self._n_cap)
         dev = runtime.device
         self._pin = dev is not None and torch.device(dev).type == "cuda"
-        n, r, g = max_tokens, self.max_requests, len(cache.kv_groups)
+        n, r, g = self._n_cap, self.max_requests, len(cache.kv_groups)
         # one staging area: [ids n][pos n][req n][logit_rows n][cu_q r+1][seq r][slot r][first r] + g * [slots n]
         self._small_len = 4 * n + 4 * r + 1 + g * n + 2 * r      # the last 2r words: temperatures, uniforms (float32)
         # two host staging sets used in turn: a set is rewritten only after the copy that
@@ -167,7 +170,9 @@ class ModelRunner:
         self.launches_per_graph_step = 0
 
     # ------------------------------------------------------------------ the step
-    def validate(self, entries: Sequence[StepEntry], placeholders: bool = False) -> None:
+    def validate(self, entries: Sequence[StepEntry], placeholders: bool = False, sampled: bool = False) -> None:
+        """Refuse a malformed batch before anything is taken or launched.  ``sampled``: the wanted rows
+        go through the sampling kernel, whose per-row inputs and outputs hold ``max_requests`` rows."""
         if not entries:
             raise BatchError("a step needs at least one entry")
         if len(entries) > self.max_requests:
@@ -195,6 +200,10 @@ class ModelRunner:
             total += n
         if total > self.max_tokens:
             raise BatchError(f"{total} tokens in a step; at most {self.max_tokens}")
+        if sampled:
+            wanted = sum(len(e.want) for e in entries)
+            if wanted > self.max_requests:
+                raise BatchError(f"{wanted} rows to sample from in a step; at most {self.max_requests}")
 
     def _reserve(self, entries) -> None:
         cache = self.cache
@@ -216,7 +225,7 @@ class ModelRunner:
         cannot all be had."""
         self.validate(entries)
         self._reserve(entries)
-        logits = self._execute(entries, None, None, None, sample=False)
+        logits = self._run_reserved(entries, None, None, None, sample=False)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
@@ -233,12 +242,12 @@ class ModelRunner:
         device (every entry then brings exactly one token, whose id in ``tokens`` is ignored)."""
         if feed is not None and (len(feed[1]) != len(entries) or any(len(e.tokens) != 1 for e in entries)):
             raise BatchError("a step fed from the device brings one token per entry and one source row per entry")
-        self.validate(entries, placeholders=feed is not None)
+        self.validate(entries, placeholders=feed is not None, sampled=True)
         wanted = sum(len(e.want) for e in entries)
         if len(temperatures) != wanted or len(uniforms) != wanted:
             raise BatchError("one temperature and one uniform number per wanted row")
         self._reserve(entries)
-        self._execute(entries, temperatures, uniforms, feed, sample=True)
+        self._run_reserved(entries, temperatures, uniforms, feed, sample=True)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
@@ -254,6 +263,18 @@ class ModelRunner:
             event = torch.cuda.Event()
             event.record()
         return SampledTokens(dev, host, event, wanted, slot)
+
+    def _run_reserved(self, entries, temperatures, uniforms, feed, sample: bool):
+        """``_execute`` for a step whose pages are taken: if it raises, the pages go back, so that a caller
+        that goes on after the error (the engine fails the step's requests; a replay ends) finds the
+        cache as it was before the step."""
+        try:
+            return self._execute(entries, temperatures, uniforms, feed, sample=sample)
+        except BaseException:
+            for e in entries:
+                if self.cache.has_request(e.request_id):
+                    self.cache.release_allocation(e.request_id)
+            raise
 
     def _apply_feed(self, ctx, feed) -> None:
         """Overwrite the step's token ids on the device with rows of the previous step's sampled ids."""
@@ -302,7 +323,7 @@ class ModelRunner:
             r_bucket = 1
             while r_bucket < len(entries):
                 r_bucket *= 2
-            r_bucket = min(r_bucket, self.max_requests)
+            r_bucket = min(r_bucket, self.max_requests)      # <= _n_cap, which the staging regions are sized by
         if not self.use_graphs:
             ctx = self._build_context(entries, pad_to=r_bucket, seq_bucket=seq_bucket, **build)
             self._apply_feed(ctx, feed)
@@ -365,7 +386,7 @@ class ModelRunner:
     # ------------------------------------------------------------------ metadata
     def _build_context(self, entries, temperatures=None, uniforms=None, pad_to=0, seq_bucket=0) -> StepContext:
         cache = self.cache
-        n_max, r_max = self.max_tokens, self.max_requests
+        n_max, r_max = self._n_cap, self.max_requests
         turn = self.steps_run % 2
         if self._stage_events[turn] is not None:
             self._stage_events[turn].synchronize()
@@ -398,6 +419,9 @@ class ModelRunner:
             for gs in group_slots:
                 gs.append(-1)
         N, R, M = len(ids), len(cu) - 1, len(rows)
+        if N > n_max or R > r_max or M > n_max:
+            raise BatchError(f"a step of {N} rows, {R} requests and {M} wanted rows does not fit the staging "
+                             f"regions ({n_max} rows, {r_max} requests)")
         h = host_small
         o_ids, o_pos, o_req, o_rows = 0, n_max, 2 * n_max, 3 * n_max
         o_cu = 4 * n_max

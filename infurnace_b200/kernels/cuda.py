@@ -62,7 +62,7 @@ class CudaKernels:
         self.scratch_generation = 0  # bumped when a scratch buffer moves: captured graphs go stale
         self.core = load_library("core", progress=progress)
         c = self.core
-        c.ifb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        c.ifb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
         c.ifb_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_void_p, c_int,
                                   c_void_p, c_int, c_int, c_void_p]
         c.ifb_qk_norm_rope_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -86,13 +86,16 @@ class CudaKernels:
         # up to here norms are folded into products (the kernels take 64 rows; beyond 32 the separate norm measured faster)
         self.fold_max_rows = int(os.environ.get("INFURNACE_FOLD_MAX_ROWS", "32"))
         self.split_min_keys = int(os.environ.get("INFURNACE_SPLIT_MIN_KEYS", "256"))   # fewest keys a split of a context gets
-        self.skinny_max_rows = 4096    # above this the plain kernel runs (until a large-tile kernel takes over)
         self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
-        self._dev_err = None           # device int: non-zero after a bounded barrier wait in a kernel gave up
+        # device int: non-zero after a kernel recorded a fault it contained (a bounded barrier wait that gave up, a
+        # token id outside the vocabulary); read by check_device_errors
+        self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.attention_tma = True      # keys and values by TMA where the sizes allow (else 16-byte async copies)
         self.attention_tc = True       # prompts on tcgen05 where the sizes allow (head size 128, pages of 16/32/64)
         self._attn_tc = None
-        self.tc_attention_calls = 0
+        self.tc_attention_calls = 0    # launches of the tcgen05 attention kernel, of the small-q kernel, and of the latter
+        self.small_q_calls = 0         # with keys and values by TMA (what ran is what tests of the product path ask)
+        self.small_q_tma_calls = 0
         self._err_armed = False
         self.tc_min_rows = 65
         self._attn_mma = {}        # head size -> library
@@ -115,8 +118,9 @@ class CudaKernels:
         if table.shape[1] != hidden or ids.numel() != n:
             raise KernelError("embed: sizes of table, ids and out do not match")
         self.launches += 1
+        self._err_armed = True
         _check(self.core.ifb_embed(table.data_ptr(), _code(table), ids.data_ptr(), out.data_ptr(), n, hidden,
-                                   self._stream()), "embed")
+                                   table.shape[0], self._dev_err.data_ptr(), self._stream()), "embed")
 
     # ------------------------------------------------------------------ norm
     def rmsnorm(self, x, weight, eps, out, delta=None, rows=None):
@@ -165,9 +169,7 @@ class CudaKernels:
                 and out.dtype in (torch.bfloat16, torch.float32):
             if n >= self.tc_min_rows:
                 return self._linear_tcgen05(x, w, out, n, o, k, epi)
-            if n <= self.gemv_max_rows:
-                return self._linear_gemv(x, w, out, n, o, k, epi)
-            return self._linear_skinny(x, w, out, n, o, k, epi)
+            return self._linear_gemv(x, w, out, n, o, k, epi)      # tc_min_rows - 1 <= gemv_max_rows
         self.launches += 1
         _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
                                          n, o, k, epi, self._stream()), "linear")
@@ -178,20 +180,22 @@ class CudaKernels:
             self._tc = load_library("linear_tcgen05", progress=self._progress)
             self._tc.ifb_linear_tcgen05.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                     c_void_p, c_int, c_void_p]
-        if self._dev_err is None:
-            self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.launches += 1
         self._err_armed = True
         _check(self._tc.ifb_linear_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), n, o, k, epi,
                                            self._dev_err.data_ptr(), int(shape), self._stream()), "linear")
 
     def check_device_errors(self):
-        """Raise if a kernel recorded that one of its bounded waits gave up (synchronises)."""
+        """Raise if a kernel recorded a fault that it contained: a bounded wait on a barrier that gave
+        up, or a token id outside the vocabulary at the embedding (synchronises)."""
         if self._err_armed:
             self._err_armed = False
             code = int(self._dev_err.item())
             if code:
                 self._dev_err.zero_()
+                if code == 900:
+                    raise KernelError("a token id outside the vocabulary reached the embedding (code 900): the step "
+                                      "that sampled it had no valid logits; its output is not valid")
                 raise KernelError(f"a kernel gave up waiting on a barrier (code {code}); its output is not valid")
 
     def _linear_gemv(self, x, w, out, n, o, k, epi, row_scale=None):
@@ -235,6 +239,8 @@ class CudaKernels:
             a.data_ptr(), w.data_ptr(), x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight), out.data_ptr(),
             partials.data_ptr(), n, o, k, self._stream()), "linear_residual_norm")
 
+    # The split-k product with scratch from the caller: not on linear()'s path (tcgen05 takes 65 rows and more, the
+    # kernel above 64 and fewer); it is the kernel whose static-scratch variant the library linear_skinny_static exports.
     def linear_splits(self, n, o, k):
         """CTAs that share the k range of one 64-feature tile: enough to cover the SMs twice, and
         at least 256 of k each."""
@@ -342,8 +348,6 @@ class CudaKernels:
             self._attn_tc.ifb_attention_tc.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
                                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                                        c_int, c_int, c_void_p]
-        if self._dev_err is None:
-            self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
         self._err_armed = True
         self.launches += 1
         self.tc_attention_calls += 1
@@ -406,8 +410,10 @@ class CudaKernels:
                 return                 # no request of this step is left for the small-q kernel
             only_small = True          # the tile kernel's requests are done; the small-q kernel takes the rest
         self.launches += 1 + (0 if only_small else 1)
-        if self._dev_err is None:
-            self._dev_err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.small_q_calls += 1
+        if self.attention_tma and head_dim % 64 == 0 and kv_pages.shape[3] in (16, 32, 64) \
+                and kv_pages.data_ptr() % 128 == 0 and kv_pages.numel() // head_dim < 0x7fffffff:
+            self.small_q_tma_calls += 1        # the library's own condition for its TMA path
         self._err_armed = True
         _check(lib.ifb_attention_mma(
             qkv.data_ptr(), qkv.stride(0), kv_pages.data_ptr(), kv_pages.shape[0], block_tables.data_ptr(),

@@ -234,3 +234,100 @@ def test_the_package_has_no_cpu_path():
     from infurnace_b200.kernels import load_cuda_kernels
     with pytest.raises(KernelError, match="no CUDA device"):
         load_cuda_kernels()
+
+
+def test_decode_padding_fits_the_staging_regions_when_slots_exceed_the_token_budget(models):
+    """A decode-only step is padded to a power-of-two number of requests.  With a token budget smaller
+    than that (3 tokens a step, 4 slots, 3 decoders) the padded step has more rows than max_tokens: the
+    staging regions are sized for it, no region runs into its neighbour, and every pad row stores nowhere."""
+    eng = engine(models["B"], "B", max_num_batched_tokens=3, max_num_seqs=4)
+    run, cache = eng.runner, eng.runner.cache
+    for rid in "abc":
+        cache.add_request(rid)
+        run.step([StepEntry(rid, [1, 2, 3])])
+    entries = [StepEntry(rid, [5], [0]) for rid in "abc"]
+    run.validate(entries, sampled=True)
+    run._reserve(entries)
+    ctx = run._build_context(entries, temperatures=[0.7] * 3, uniforms=[0.5] * 3, pad_to=4, seq_bucket=256)
+    assert ctx.num_tokens == 4 and ctx.num_requests == 4
+    for gi in range(len(cache.kv_groups)):
+        slots = ctx.group_slot_mapping[gi].tolist()
+        assert slots[3] == -1 and all(s >= 0 for s in slots[:3])
+    assert ctx.positions.tolist() == [3, 3, 3, 0] and ctx.token_ids.tolist() == [5, 5, 5, 0]
+    assert ctx.cu_q.tolist() == [0, 1, 2, 3, 4] and ctx.seq_lens.tolist() == [4, 4, 4, 0]
+    assert ctx.logit_rows.tolist() == [0, 1, 2, 0]
+    assert ctx.temperatures.tolist()[:4] == pytest.approx([0.7, 0.7, 0.7, 0.0])
+    views = [ctx.token_ids, ctx.positions, ctx.req_index, ctx.logit_rows, ctx.cu_q, ctx.seq_lens, ctx.state_slots,
+             ctx.first_portion, *ctx.group_slot_mapping, ctx.temperatures, ctx.uniforms]
+    spans = sorted((v.data_ptr(), v.data_ptr() + v.numel() * 4) for v in views)
+    assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:])), "staging regions overlap"
+    for e in entries:
+        cache.release_allocation(e.request_id)
+    # and the same through the engine: four requests decoding under a budget of three tokens a step
+    cfg, w = P.read_model(models["B"])
+    eng2 = engine(models["B"], "B", max_num_batched_tokens=3, max_num_seqs=4)
+    prompts = [tiny.random_tokens(320, n, 70 + n) for n in (4, 2, 5, 3)]
+    outs = eng2.generate(prompts, SamplingParams(max_tokens=6))
+    for p, o in zip(prompts, outs):
+        assert o == P.greedy(cfg, w, p, 6)
+    eng2.runner.cache.check()
+
+
+def test_more_sampled_rows_than_requests_are_refused_before_pages_are_taken(models):
+    eng = engine(models["A"], "A", max_num_seqs=2)
+    run, cache = eng.runner, eng.runner.cache
+    cache.add_request("a")
+    free = cache.free_pages()
+    with pytest.raises(BatchError, match="rows to sample"):
+        run.step_and_sample([StepEntry("a", [1, 2, 3, 4], [0, 1, 2])], [0.0] * 3, [0.0] * 3)
+    assert cache.free_pages() == free
+    assert run.step([StepEntry("a", [1, 2, 3, 4], [0, 1, 2])]).shape[0] == 3      # logits alone may be wanted anywhere
+
+
+def test_a_step_that_raises_gives_its_pages_back(models, monkeypatch):
+    eng = engine(models["A"], "A")
+    run, cache = eng.runner, eng.runner.cache
+    cache.add_request("a")
+    run.step([StepEntry("a", [1, 2, 3])])
+    free = cache.free_pages()
+    monkeypatch.setattr(run.model, "forward", lambda ctx: (_ for _ in ()).throw(RuntimeError("kernel refused")))
+    with pytest.raises(RuntimeError, match="kernel refused"):
+        run.step([StepEntry("a", list(range(40)), [39])])
+    assert cache.free_pages() == free and cache.num_computed("a") == 3
+    cache.check()
+
+
+def test_a_fault_recorded_on_the_device_fails_the_requests_that_ran(models):
+    """The kernels' error word is read every 32 steps and before a request is reported finished.  When it
+    is set, every request that ran since it was last read clean fails, with its pages and slot given
+    back, and the engine goes on with new requests.  The fault is injected on the host: the stand-in
+    kernel set raises from ``check_device_errors`` as the CUDA kernel set does for a non-zero word."""
+    class Faulty(ReferenceKernels):
+        armed = False
+
+        def check_device_errors(self):
+            if self.armed:
+                self.armed = False
+                raise KernelError("a kernel gave up waiting on a barrier (code 7); its output is not valid")
+
+    kernels = Faulty()
+    opts = EngineOptions(dtype="float32", device="cpu", page_size=16, num_pages=40, max_num_seqs=4, max_num_batched_tokens=64)
+    eng = Engine.from_model_dir(models["A"], opts, kernels=kernels)
+    eng.add_request(Request("long", [1, 2, 3], SamplingParams(max_tokens=60)))
+    eng.add_request(Request("short", [4, 5], SamplingParams(max_tokens=3)))
+    eng.step()
+    kernels.armed = True
+    failed = []
+    for _ in range(10):
+        res = eng.step()
+        failed += list(res.failed_requests)
+        assert "short" not in res.completed_requests          # it is not reported finished on poisoned output
+        if eng.is_done():
+            break
+    assert sorted(failed) == ["long", "short"]
+    for rid in ("long", "short"):
+        r = eng.scheduler.get_request(rid)
+        assert r.state is RequestState.FAILED and "code 7" in r.error
+    assert eng.is_done() and eng.runner.cache.free_pages() == [40]
+    eng.runner.cache.check()
+    assert len(eng.generate([[7, 8, 9]], SamplingParams(max_tokens=4))[0]) == 4

@@ -147,3 +147,30 @@ def test_launching_ahead_changes_no_token_on_the_gpu(models, dtype):
         assert eng.is_done() and eng.runner.graph_replays > 0
     assert outs[True] == outs[False]
     assert any(len(o) < sp.max_tokens for o, sp in zip(outs[True], sps))
+
+
+def test_a_fault_recorded_in_the_error_word_fails_the_requests_that_ran(models):
+    """The device error word set between steps (written from the host here; no kernel is made to give up): the
+    requests that ran since it was last read clean end FAILED with their pages and slots back, none of them is
+    reported finished, and the engine serves the next request."""
+    eng = engine(models["B"], "B", "bfloat16")
+    eng.add_request(Request("long", tiny.random_tokens(320, 9, 1), SamplingParams(max_tokens=50)))
+    eng.add_request(Request("short", tiny.random_tokens(320, 5, 2), SamplingParams(max_tokens=3)))
+    eng.step()
+    K = eng.runner.rt.kernels
+    torch.cuda.synchronize()
+    K._dev_err.fill_(7)
+    failed, completed = [], []
+    for _ in range(10):
+        res = eng.step()
+        failed += list(res.failed_requests)
+        completed += list(res.completed_requests)
+        if eng.is_done():
+            break
+    assert sorted(failed) == ["long", "short"] and not completed
+    for rid in ("long", "short"):
+        r = eng.scheduler.get_request(rid)
+        assert r.state is RequestState.FAILED and "code 7" in r.error
+    assert eng.is_done() and eng.runner.cache.free_pages() == [64, 64]
+    eng.runner.cache.check()
+    assert len(eng.generate([tiny.random_tokens(320, 4, 3)], SamplingParams(max_tokens=4))[0]) == 4

@@ -41,6 +41,36 @@ def test_embed(K, dtype, n, hidden, vocab):
     assert torch.equal(out.cpu(), table[ids.long()].float())
 
 
+def test_a_row_without_valid_logits_cannot_send_the_embedding_out_of_range(K):
+    """A row of logits that is all NaN (any NaN in the residual stream) still samples an id inside the
+    vocabulary, on the greedy and on the temperature path; and an id outside the vocabulary that does reach
+    the embedding (ids fed on the device are never seen by the host) reads nothing: zeros are written and
+    the error word says so."""
+    vocab, hidden = 333, 72
+    logits = rnd((4, vocab), torch.float32, 5).cuda()
+    logits[1] = float("nan")
+    logits[3, 10:] = float("nan")
+    out = torch.full((4,), -7, dtype=torch.int32, device="cuda")
+    K.sample(logits, None, None, out)
+    assert all(0 <= t < vocab for t in out.tolist()) and out[1].item() == 0
+    temp = torch.tensor([0.7, 0.7, 0.0, 1.3], device="cuda")
+    uni = torch.tensor([0.3, 0.9, 0.5, 0.99], device="cuda")
+    out.fill_(-7)
+    K.sample(logits, temp, uni, out)
+    assert all(0 <= t < vocab for t in out.tolist())
+    table = rnd((vocab, hidden), torch.bfloat16, 6).cuda()
+    ids = torch.tensor([5, vocab, -1, 0x7fffffff, vocab - 1], dtype=torch.int32, device="cuda")
+    x = torch.full((5, hidden), 9.0, dtype=torch.float32, device="cuda")
+    K.check_device_errors()
+    K.embed(table, ids, x)
+    assert torch.equal(x[0], table[5].float()) and torch.equal(x[4], table[vocab - 1].float())
+    assert float(x[1:4].abs().max()) == 0.0
+    from infurnace_b200.errors import KernelError
+    with pytest.raises(KernelError, match="outside the vocabulary"):
+        K.check_device_errors()
+    K.check_device_errors()          # the word was cleared
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("wdtype", DTYPES)
 @pytest.mark.parametrize("n,hidden,splits", [(1, 72, 0), (5, 1000, 1), (33, 3001, 3), (90, 1024, 1), (64, 128, 0), (70, 2048, 2),

@@ -100,10 +100,11 @@ def schedule_portions(requests, seed=0):
     return steps
 
 
-def schedule_mixed(requests, max_live=4, max_tokens=256, tail=12, seed=0, unit=64):
-    """Up to ``max_live`` requests at a time: portions of some beside single decoded tokens
-    of others, a request sometimes left out of a step, under a pool of ``max_tokens`` tokens
-    (each live request counted rounded up to ``unit``), so that pages are used again."""
+def schedule_mixed(requests, max_live=4, max_tokens=256, tail=12, seed=0, unit=64, sizes=(2, 3, 5, 8, 13, 16, 21)):
+    """Up to ``max_live`` requests at a time: portions of some (of the ``sizes``) beside single
+    decoded tokens of others, a request sometimes left out of a step, under a pool of
+    ``max_tokens`` tokens (each live request counted rounded up to ``unit``), so that pages are
+    used again."""
     rng = random.Random(seed)
     waiting = list(requests.items())
     live = {}      # rid -> progress
@@ -123,7 +124,7 @@ def schedule_mixed(requests, max_live=4, max_tokens=256, tail=12, seed=0, unit=6
         for rid in chosen:
             toks, s = requests[rid], live[rid]
             left = len(toks) - s
-            n = 1 if left <= tail else min(left - tail, rng.choice([2, 3, 5, 8, 13, 16, 21]))
+            n = 1 if left <= tail else min(left - tail, rng.choice(list(sizes)))
             entries.append(_entry(rid, toks, s, n))
             live[rid] = s + n
             if s + n == len(toks):
