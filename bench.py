@@ -163,7 +163,7 @@ def prefill_flops(cfg, tokens):
     return linear + attn + head
 
 
-def time_decode(runner, sampler, rids, vocab, steps, warmup, seed=1):
+def time_decode(runner, rids, vocab, steps, warmup, seed=1):
     """Device time of ``steps`` decode steps (ms), each step: step function + sampling kernel."""
     import torch
     from infurnace_b200.engine.runner import StepEntry
@@ -198,7 +198,6 @@ def run_ours(args):
     from infurnace_b200.engine import Engine, EngineOptions, Request, SamplingParams
     from infurnace_b200.engine.runner import StepEntry
     from infurnace_b200.models import read_config
-    from infurnace_b200.sampling import Sampler
     from infurnace_b200.weights.random_init import write_random_model
 
     hbm_peak, tf_peak, peak_src = read_peaks()
@@ -232,7 +231,6 @@ def run_ours(args):
         print(json.dumps({"mode": "prefill", "tokens": PREFILL_TOKENS, "steps": max(1, steps),
                           "ms_median": statistics.median(times), "ms_min": min(times)}))
         return 0
-    sampler = Sampler(runner.rt.kernels, runner.rt.device)
     randomize_pages(runner)
     torch.cuda.synchronize()
     start_ctx = CONTEXT - warmup - steps
@@ -241,7 +239,7 @@ def run_ours(args):
     clocks = ClockSampler()
     rids = fill_contexts(runner, batch, start_ctx)
     clocks.start()
-    ms, launches = time_decode(runner, sampler, rids, cfg.vocab_size, steps, warmup)
+    ms, launches = time_decode(runner, rids, cfg.vocab_size, steps, warmup)
     clock_report = clocks.stop()
     release(runner, rids)
     ms_per_step = ms / steps
@@ -282,7 +280,7 @@ def run_ours(args):
     for b in (1, 64):
         k = max(8, steps // 2)
         rids = fill_contexts(runner, b, CONTEXT - warmup - k)
-        pms, _ = time_decode(runner, sampler, rids, cfg.vocab_size, k, warmup)
+        pms, _ = time_decode(runner, rids, cfg.vocab_size, k, warmup)
         release(runner, rids)
         points[f"decode_b{b}"] = b * k / (pms / 1000.0)
 

@@ -181,11 +181,15 @@ class EmbeddingSpec:
 @dataclass(frozen=True)
 class LMHeadSpec:
     """logits = x @ W^T in 32-bit (model.py:151).  ``tied`` True: ``weight`` names the
-    embedding table, which is read in place (weights.py:68), and is no tensor of its own."""
+    embedding table, which is read in place (weights.py:68), and is no tensor of its own;
+    ``stored_as`` is then the name under which a model folder may nevertheless store the
+    head, which is accepted only as an exact copy of the table (the reference's rule is
+    identity of the two, model.py:34-36)."""
     vocab_size: int
     hidden_size: int
     weight: str
     tied: bool
+    stored_as: Optional[str] = None
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         if self.tied:
@@ -240,6 +244,13 @@ class ModelPlan:
             if not call.store and call.cache not in stored:
                 raise ValueError(f"layer call reads cache {call.cache}, which no call stores")
         return tuple(out)
+
+    def duplicates(self) -> Mapping[str, str]:
+        """Names a model folder may hold beside the inventory, each with the tensor it must be an exact
+        copy of: the head of a tied model stored under a name of its own."""
+        if self.lm_head.tied and self.lm_head.stored_as and self.lm_head.stored_as != self.lm_head.weight:
+            return {self.lm_head.stored_as: self.lm_head.weight}
+        return {}
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         t = dict(self.embedding.tensors())

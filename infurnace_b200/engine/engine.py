@@ -22,7 +22,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 from ..errors import KernelError, OutOfPages
-from ..sampling import Sampler, uniform
+from ..sampling import uniform
 from ..tokenizer import StreamingDetokenizer, Tokenizer, check_stop_strings
 from .loading import EngineOptions, build_runner
 from .request import Request, RequestMetrics, RequestState, SamplingParams
@@ -55,12 +55,11 @@ class RawStep:
 
 
 class Engine:
-    def __init__(self, runner, scheduler: Optional[Scheduler] = None, sampler: Optional[Sampler] = None,
+    def __init__(self, runner, scheduler: Optional[Scheduler] = None,
                  tokenizer: Optional[Tokenizer] = None, eos_token_ids: Sequence[int] = (), max_prefill_portion=None):
         self.runner = runner
         self.scheduler = scheduler or Scheduler(runner.cache, runner.max_requests, runner.max_tokens,
                                                 runner.max_model_len, max_prefill_portion)
-        self.sampler = sampler or Sampler(runner.rt.kernels, runner.rt.device)   # for callers that hold logits
         self.tokenizer = tokenizer
         self.eos_token_ids = list(eos_token_ids)
         self._detoks: Dict[str, StreamingDetokenizer] = {}

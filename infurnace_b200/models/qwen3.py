@@ -64,7 +64,7 @@ def build_qwen3_plan(cfg: Qwen3Config) -> ModelPlan:
         final_norm=RMSNormSpec(cfg.hidden_size, cfg.rms_norm_eps, "model.norm.weight"),
         lm_head=LMHeadSpec(cfg.vocab_size, cfg.hidden_size,
                            embed_name if cfg.tie_word_embeddings else "lm_head.weight",
-                           tied=cfg.tie_word_embeddings),
+                           tied=cfg.tie_word_embeddings, stored_as="lm_head.weight"),
     )
 
 

@@ -30,6 +30,9 @@ def uniform(seed: int, counter: int) -> float:
 
 
 class Sampler:
+    """For callers that hold logits of their own (from ``ModelRunner.step``): the same kernel and the
+    same random numbers as the engine, which samples inside ``step_and_sample`` without this class."""
+
     def __init__(self, kernels, device):
         self.k = kernels
         self.device = device

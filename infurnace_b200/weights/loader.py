@@ -4,7 +4,10 @@ The rule is the reference's (src/infurnace/executor/tinygrad/weights.py:42-55): 
 of names in the files must equal the inventory, every shape must match, and all of this
 is checked before any tensor is read or converted
 (tests/test_model_weights.py:80-103).  One :class:`WeightError` lists everything that is
-wrong: missing tensors, unexpected tensors and wrong shapes.
+wrong: missing tensors, unexpected tensors and wrong shapes.  One exception to "equal":
+a tied model's folder may also store the head under its own name; the reference demands
+that head and embedding be one object (weights.py:68, model.py:34-36), so here the stored
+head is accepted if it equals the embedding table bit for bit, and is an error otherwise.
 
 Dtypes.  In bfloat16 mode a floating tensor is kept in bfloat16, except that a tensor
 stored in 32-bit stays in 32-bit (float16 is converted to bfloat16); in float32 mode
@@ -23,11 +26,18 @@ _FLOAT_TAGS = {"F64", "F32", "F16", "BF16"}
 _INT_TAGS = {"I64", "I32", "I16", "I8", "U8"}
 
 
-def check_inventory(found: Mapping[str, tuple], expected: Mapping[str, "object"]) -> None:
-    """``found``: name -> (dtype tag, shape).  Raises one error naming every fault."""
+def check_inventory(found: Mapping[str, tuple], expected: Mapping[str, "object"],
+                    duplicates: Mapping[str, str] = {}) -> None:
+    """``found``: name -> (dtype tag, shape).  ``duplicates``: names that may be present beside the
+    inventory, each with the tensor it must copy (same shape and dtype here; the bytes are compared by
+    the caller).  Raises one error naming every fault."""
     missing = sorted(set(expected) - set(found))
-    unexpected = sorted(set(found) - set(expected))
+    unexpected = sorted(set(found) - set(expected) - set(duplicates))
     wrong = []
+    for name, of in sorted(duplicates.items()):
+        if name in found and of in found and tuple(found[name]) != tuple(found[of]):
+            wrong.append(f"{name}: stored beside {of}, which it must equal, as {found[name][0]} {tuple(found[name][1])} "
+                         f"against {found[of][0]} {tuple(found[of][1])}")
     for name in sorted(set(expected) & set(found)):
         tag, shape = found[name]
         spec = expected[name]
@@ -72,7 +82,14 @@ def load_weights(model_dir: str, plan, engine_dtype, device, progress=None) -> D
         if dup:
             raise WeightError("tensors stored twice: " + ", ".join(sorted(dup)))
         expected = plan.tensors()
-        check_inventory(found, expected)
+        duplicates = plan.duplicates() if hasattr(plan, "duplicates") else {}
+        check_inventory(found, expected, duplicates)
+        for name, of in sorted(duplicates.items()):
+            if name in found:
+                a, b = owner[name].tensor(name), owner[of].tensor(of)
+                if not torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8)):
+                    raise WeightError(f"weights do not match the model: unexpected tensors (1): {name} (the model ties it to "
+                                      f"{of}, and the two differ)")
         out = {}
         last = time.monotonic()
         for i, (name, spec) in enumerate(expected.items()):

@@ -174,3 +174,24 @@ def test_a_fault_recorded_in_the_error_word_fails_the_requests_that_ran(models):
     assert eng.is_done() and eng.runner.cache.free_pages() == [64, 64]
     eng.runner.cache.check()
     assert len(eng.generate([tiny.random_tokens(320, 4, 3)], SamplingParams(max_tokens=4))[0]) == 4
+
+
+def test_sampler_for_callers_that_hold_logits_draws_what_the_engine_draws(models):
+    """``Sampler`` on the logits of ``ModelRunner.step`` gives the token the engine samples inside its
+    step: the same kernel and the same (seed, counter) numbers."""
+    from infurnace_b200.engine.runner import StepEntry
+    from infurnace_b200.sampling import Sampler
+    prompt = tiny.random_tokens(320, 21, 9)
+    sp = SamplingParams(max_tokens=6, temperature=0.8, seed=77)
+    want = engine(models["B"], "B", "float32").generate([prompt], sp)[0]
+    eng = engine(models["B"], "B", "float32")
+    run = eng.runner
+    sampler = Sampler(run.rt.kernels, run.rt.device)
+    run.cache.add_request("x")
+    toks, got = list(prompt), []
+    for k in range(6):
+        logits = run.step([StepEntry("x", toks, [len(toks) - 1])])
+        got += sampler.sample(logits, [0.8], [77], [k])
+        toks = [got[-1]]
+    assert got == want
+    assert sampler.sample(logits, [0.0], [0], [0]) == [int(logits[0].argmax())]

@@ -86,12 +86,31 @@ def test_nothing_is_read_before_the_check(folder, monkeypatch):
     assert reads == []       # the reference checks before any cast too (tests/test_model_weights.py:80-103)
 
 
-def test_tied_model_refuses_a_separate_head(tmp_path):
+def test_tied_model_takes_a_stored_head_only_as_a_copy_of_the_embedding(tmp_path):
+    """The reference demands that head and embedding be one object (weights.py:68, model.py:34-36): a folder
+    of a tied model that also stores lm_head.weight loads if the two are equal bit for bit, and the head
+    then reads the embedding table; a head that differs, in value, dtype or shape, is an error."""
     cfg = config_from_dict(tiny.TINY["A"]["config"])
+    plan = plan_for(cfg)
     d = write_random_model(cfg, 1, str(tmp_path / "a"))
     _rewrite(d, lambda t: t.__setitem__("lm_head.weight", t["model.embed_tokens.weight"].clone()))
-    with pytest.raises(WeightError, match="unexpected tensors.*lm_head.weight"):
-        load_weights(d, plan_for(cfg), torch.bfloat16, "cpu")
+    w = load_weights(d, plan, torch.bfloat16, "cpu")
+    assert "lm_head.weight" not in w and plan.lm_head.weight == "model.embed_tokens.weight"
+
+    def nudge(t):
+        h = t["model.embed_tokens.weight"].clone()
+        h[3, 5] += 1.0
+        t["lm_head.weight"] = h
+    _rewrite(d, nudge)
+    with pytest.raises(WeightError, match="unexpected tensors.*lm_head.weight.*differ"):
+        load_weights(d, plan, torch.bfloat16, "cpu")
+    _rewrite(d, lambda t: t.__setitem__("lm_head.weight", t["model.embed_tokens.weight"].float()))
+    with pytest.raises(WeightError, match="lm_head.weight: stored beside"):
+        load_weights(d, plan, torch.bfloat16, "cpu")
+    # an untied model still needs its head, and a tied one accepts no other stranger
+    _rewrite(d, lambda t: (t.pop("lm_head.weight"), t.__setitem__("extra.weight", torch.zeros(2))))
+    with pytest.raises(WeightError, match="unexpected tensors.*extra.weight"):
+        load_weights(d, plan, torch.bfloat16, "cpu")
 
 
 def test_dtype_policy(tmp_path):

@@ -10,7 +10,7 @@ import torch
 
 QWEN3 = "Qwen3ForCausalLM"
 
-# Three configurations that differ in every size and option.
+# Configurations that differ in every size and option.
 TINY = {
     # 2 layers, every key visible, tied head, float32 storage
     "A": dict(config=dict(architectures=[QWEN3], num_hidden_layers=2, hidden_size=64, num_attention_heads=4,
@@ -25,6 +25,12 @@ TINY = {
                           max_position_embeddings=256, sliding_window=24,
                           layer_types=["full_attention", "sliding_attention", "full_attention"]),
               page_size=8, store_dtype="bfloat16", seed=22),
+    # the same sizes without any window
+    "B0": dict(config=dict(architectures=[QWEN3], num_hidden_layers=3, hidden_size=96, num_attention_heads=8,
+                           num_key_value_heads=2, head_dim=32, intermediate_size=160, vocab_size=320,
+                           rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                           max_position_embeddings=256),
+               page_size=8, store_dtype="float32", seed=22),
     # nothing is a power of two: 6 heads in 3 groups of head size 48, widths 72/136, vocabulary 333,
     # windows on the first and last layer, norm weights stored in float32 beside bfloat16 matrices
     "C": dict(config=dict(architectures=[QWEN3], num_hidden_layers=4, hidden_size=72, num_attention_heads=6,
