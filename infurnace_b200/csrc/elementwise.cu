@@ -34,6 +34,44 @@ IFB_EXPORT int ifb_embed(const void* table, int table_dtype, const int* ids, flo
 }
 
 // ------------------------------------------------------------------------------------------
+// random_normal: out[i] = mean + std * z_i, z_i approximately N(0, 1), a pure function of (seed, i).
+// z_i is the sum of twelve 16-bit integers, taken from three 64-bit words of a counter-based mixer at counters
+// 3i, 3i+1, 3i+2, minus its mean, over 65536: integer arithmetic and then one exact scaling, one rounded multiply and
+// one rounded addition (never contracted into a fused multiply-add), so that a host program doing the same steps in
+// float32 gets the same bits.  The sum of twelve uniform terms has variance 1 and reaches +-6.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long rnd_mix(unsigned long long z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+template <typename T>
+__global__ void random_normal_kernel(T* __restrict__ out, long long n, unsigned long long seed, float mean, float std) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    int sum = 0;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const unsigned long long z = rnd_mix(seed + (3ull * (unsigned long long)i + j) * 0x9E3779B97F4A7C15ull);
+      sum += (int)(z & 0xFFFF) + (int)((z >> 16) & 0xFFFF) + (int)((z >> 32) & 0xFFFF) + (int)(z >> 48);
+    }
+    const float zf = (float)(sum - 393210) * (1.0f / 65536.0f);
+    out[i] = from_f32<T>(__fadd_rn(mean, __fmul_rn(std, zf)));
+  }
+}
+
+IFB_EXPORT int ifb_random_normal(void* out, int dtype, long long n, unsigned long long seed, float mean, float std,
+                                 cudaStream_t stream) {
+  if (n <= 0) return IFB_OK;
+  const unsigned blocks = (unsigned)((n + 1023) / 1024 < 148 * 16 ? (n + 1023) / 1024 : 148 * 16);
+  if (dtype == IFB_F32) random_normal_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, n, seed, mean, std);
+  else if (dtype == IFB_BF16) random_normal_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, n, seed, mean, std);
+  else return IFB_ERR_DTYPE;
+  return ifb_launch_status();
+}
+
+// ------------------------------------------------------------------------------------------
 // rmsnorm: v = x[row] + sum_s delta[s][row];  out = v * rsqrt(mean(v^2) + eps) * w
 // Without `rows`, row = blockIdx.x and v is written back to x.  With `rows`, row = rows[blockIdx.x]
 // and x stays as it is.  One block per output row; v is kept in shared memory between the passes.

@@ -15,7 +15,6 @@ that ran since the error word was last read clean.
 """
 from __future__ import annotations
 
-import tempfile
 import time
 import traceback
 from dataclasses import dataclass, field
@@ -86,19 +85,30 @@ class Engine:
 
     @classmethod
     def from_random(cls, config, seed: int, options: Optional[EngineOptions] = None, store_dtype="bfloat16",
-                    workdir: Optional[str] = None, **kw) -> "Engine":
-        """Random weights for ``config`` (a typed configuration or a config.json mapping) from
-        ``seed``: a model folder is written (to ``workdir`` or a temporary folder) and loaded."""
+                    workdir: Optional[str] = None, tokenizer=None, eos_token_ids: Sequence[int] = (), kernels=None,
+                    progress=None, **overrides) -> "Engine":
+        """Random weights for ``config`` (a typed configuration or a config.json mapping) from ``seed``.
+        Without ``workdir`` the tensors are drawn on the device, no file is written, and a model of any
+        size that fits the device can be made; with ``workdir`` a model folder is written there and
+        loaded.  Both give the same tensors."""
         from ..models import config_from_dict
-        from ..weights.random_init import write_random_model
         if isinstance(config, Mapping):
             config = config_from_dict(config)
-        if workdir is None:
-            with tempfile.TemporaryDirectory(prefix="infurnace_b200_") as d:
-                write_random_model(config, seed, d, store_dtype=store_dtype)
-                return cls.from_model_dir(d, options, **kw)
-        write_random_model(config, seed, workdir, store_dtype=store_dtype)
-        return cls.from_model_dir(workdir, options, **kw)
+        if workdir is not None:
+            from ..weights.random_init import write_random_model
+            write_random_model(config, seed, workdir, store_dtype=store_dtype)
+            return cls.from_model_dir(workdir, options, tokenizer=tokenizer, eos_token_ids=eos_token_ids, kernels=kernels,
+                                      progress=progress, **overrides)
+        options = options or EngineOptions()
+        for k, v in overrides.items():
+            if not hasattr(options, k):
+                raise TypeError(f"unknown engine option {k!r}")
+            setattr(options, k, v)
+        config, plan, runner = build_runner(None, options, kernels=kernels, progress=progress,
+                                            random=(config, seed, store_dtype))
+        eng = cls(runner, tokenizer=tokenizer, eos_token_ids=eos_token_ids)
+        eng.config, eng.plan, eng.options = config, plan, options
+        return eng
 
     # ------------------------------------------------------------------ offline request API
     def add_request(self, req: Request) -> None:

@@ -38,17 +38,25 @@ def parse_dtype(name):
         raise ModelConfigError(f"dtype {name!r}: choose bfloat16 or float32") from None
 
 
-def build_runner(model_dir: str, options: EngineOptions, kernels=None, progress=None):
+def build_runner(model_dir: Optional[str], options: EngineOptions, kernels=None, progress=None, random=None):
     """(config, plan, runner) for the model folder.  ``kernels`` None loads the CUDA kernel
-    set, which fails loudly without a GPU or a compiler; tests may pass a stand-in."""
+    set, which fails loudly without a GPU or a compiler; tests may pass a stand-in.
+
+    ``random`` = (config, seed, store_dtype name): no folder is read; the tensors are drawn on the
+    device as the parts ask for them (weights/random_init.py), which is how models too large to pass
+    through a file get their random weights."""
     dtype = parse_dtype(options.dtype)
-    config = read_config(model_dir)
+    config = read_config(model_dir) if random is None else random[0]
     plan = plan_for(config)
     if kernels is None:
         from ..kernels import load_cuda_kernels
         kernels = load_cuda_kernels(progress=progress)
     runtime = Runtime(device=torch.device(options.device), act_dtype=dtype, kernels=kernels)
-    weights = load_weights(model_dir, plan, dtype, runtime.device, progress=progress)
+    if random is None:
+        weights = load_weights(model_dir, plan, dtype, runtime.device, progress=progress)
+    else:
+        from ..weights.random_init import DeviceRandomWeights
+        weights = DeviceRandomWeights(plan, random[1], dtype, runtime.device, kernels, store_dtype=parse_dtype(random[2]))
     model = DecoderModel(plan, weights, runtime)
     del weights
     max_len = min(options.max_model_len or plan.max_positions, plan.max_positions)

@@ -63,6 +63,7 @@ class CudaKernels:
         self.core = load_library("core", progress=progress)
         c = self.core
         c.ifb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+        c.ifb_random_normal.argtypes = [c_void_p, c_int, c_longlong, ctypes.c_ulonglong, c_float, c_float, c_void_p]
         c.ifb_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_void_p, c_int,
                                   c_void_p, c_int, c_int, c_void_p]
         c.ifb_qk_norm_rope_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -121,6 +122,14 @@ class CudaKernels:
         self._err_armed = True
         _check(self.core.ifb_embed(table.data_ptr(), _code(table), ids.data_ptr(), out.data_ptr(), n, hidden,
                                    table.shape[0], self._dev_err.data_ptr(), self._stream()), "embed")
+
+    def random_normal(self, out, seed64, mean, std):
+        """out[i] = mean + std * z_i with z_i approximately N(0, 1), a pure function of (seed64, i): the
+        same bits as ``weights.random_init.normal_values``."""
+        _dense(out, "out")
+        self.launches += 1
+        _check(self.core.ifb_random_normal(out.data_ptr(), _code(out), out.numel(), int(seed64) & ((1 << 64) - 1),
+                                           float(mean), float(std), self._stream()), "random_normal")
 
     # ------------------------------------------------------------------ norm
     def rmsnorm(self, x, weight, eps, out, delta=None, rows=None):

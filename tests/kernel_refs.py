@@ -26,6 +26,11 @@ class ReferenceKernels:
     def embed(self, table, ids, out):
         out.copy_(table[ids.long()].to(out.dtype))
 
+    def random_normal(self, out, seed64, mean, std):
+        """out[i] = mean + std * z_i, the counter-based values of weights/random_init.py."""
+        from infurnace_b200.weights.random_init import normal_values
+        out.copy_(normal_values(seed64, out.numel(), mean, std).view(out.shape).to(out.dtype))
+
     # ------------------------------------------------------------------ norm
     def rmsnorm(self, x, weight, eps, out, delta=None, rows=None):
         """x is the float32 residual stream [N, H]; delta ([N, H] or [S, N, H], summed over S)

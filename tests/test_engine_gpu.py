@@ -195,3 +195,19 @@ def test_sampler_for_callers_that_hold_logits_draws_what_the_engine_draws(models
         toks = [got[-1]]
     assert got == want
     assert sampler.sample(logits, [0.0], [0], [0]) == [int(logits[0].argmax())]
+
+
+def test_random_weights_drawn_on_the_device_equal_the_folders(tmp_path):
+    """``Engine.from_random`` without a folder (tensors drawn by the kernel as the parts ask for them) against
+    the folder writer on the host followed by the loader: the same fused matrices, the same tokens."""
+    from infurnace_b200.models import config_from_dict
+    cfg = config_from_dict(tiny.TINY["C"]["config"])
+    opts = dict(dtype="bfloat16", page_size=32, num_pages=16, max_num_seqs=2, max_num_batched_tokens=64)
+    a = Engine.from_random(cfg, 4, EngineOptions(**opts))
+    b = Engine.from_random(cfg, 4, EngineOptions(**opts), workdir=str(tmp_path / "m"))
+    for la, lb in zip(a.runner.model.layers, b.runner.model.layers):
+        assert torch.equal(la.mixer.w_qkv, lb.mixer.w_qkv) and torch.equal(la.ffn.w_gate_up, lb.ffn.w_gate_up)
+        assert torch.equal(la.mixer_norm.weight, lb.mixer_norm.weight)
+    assert a.runner.model.lm_head.weight.data_ptr() == a.runner.model.embedding.table.data_ptr()      # tied: one tensor
+    prompt = tiny.random_tokens(333, 12, 1)
+    assert a.generate([prompt], SamplingParams(max_tokens=8)) == b.generate([prompt], SamplingParams(max_tokens=8))

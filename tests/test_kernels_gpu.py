@@ -41,6 +41,19 @@ def test_embed(K, dtype, n, hidden, vocab):
     assert torch.equal(out.cpu(), table[ids.long()].float())
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_random_normal_gives_the_hosts_bits(K, dtype):
+    """The device's counter-based values equal the host's bit for bit (integer sum, exact scaling, one rounded
+    multiply, one rounded addition), for a matrix (mean 0) and a norm weight (mean 1), at a length that is no
+    multiple of anything."""
+    from infurnace_b200.weights.random_init import normal_values, tensor_seed
+    for name, n, mean, std in (("a.weight", 100_003, 0.0, 0.02), ("b.weight", 4097, 1.0, 0.1)):
+        seed = tensor_seed(7, name)
+        out = torch.empty(n, dtype=dtype, device="cuda")
+        K.random_normal(out, seed, mean, std)
+        assert torch.equal(out.cpu(), normal_values(seed, n, mean, std).to(dtype))
+
+
 def test_a_row_without_valid_logits_cannot_send_the_embedding_out_of_range(K):
     """A row of logits that is all NaN (any NaN in the residual stream) still samples an id inside the
     vocabulary, on the greedy and on the temperature path; and an id outside the vocabulary that does reach

@@ -36,7 +36,8 @@ def model(request, tmp_path_factory):
     d.update(changes)
     cfg = config_from_dict(d)
     path = str(tmp_path_factory.mktemp("real") / "m")
-    write_random_model(cfg, 3, path)
+    from infurnace_b200.kernels import load_cuda_kernels
+    write_random_model(cfg, 3, path, kernels=load_cuda_kernels())        # drawn on the device: the same values, in seconds
     file = os.path.join(path, "model.safetensors")
     t = load_file(file)
     for k in list(t):                      # peaked attention, as in the tiny models
@@ -88,7 +89,8 @@ def small_06b(tmp_path_factory):
         d = json.load(f)
     d.update(num_hidden_layers=2, vocab_size=4096)
     path = str(tmp_path_factory.mktemp("cut") / "m")
-    write_random_model(config_from_dict(d), 5, path)
+    from infurnace_b200.kernels import load_cuda_kernels
+    write_random_model(config_from_dict(d), 5, path, kernels=load_cuda_kernels())
     file = os.path.join(path, "model.safetensors")
     t = load_file(file)
     for k in list(t):
@@ -101,7 +103,7 @@ def small_06b(tmp_path_factory):
     return path, cfg, w, reqs, ref
 
 
-@pytest.mark.parametrize("dtype,tolerance", [("float32", 2e-5), ("bfloat16", 0.05)])   # times the size of the largest logit
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 2e-5), ("bfloat16", 0.04)])   # times the size of the largest logit
 @pytest.mark.parametrize("mode", ["whole", "bulk_tail", "portions", "mixed"])
 def test_cutting_modes_at_the_real_head_size(small_06b, mode, dtype, tolerance):
     from infurnace_b200.engine.loading import EngineOptions, build_runner

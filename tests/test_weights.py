@@ -171,3 +171,31 @@ def test_broken_files(tmp_path):
     empty.mkdir()
     with pytest.raises(WeightError, match="no .safetensors"):
         load_weights(str(empty), None, torch.float32, "cpu")
+
+
+def test_random_values_are_counter_based_and_roughly_normal():
+    from infurnace_b200.weights.random_init import normal_values, tensor_seed
+    s = tensor_seed(3, "model.layers.0.mlp.up_proj.weight")
+    a = normal_values(s, 200_000, 0.0, 0.02)
+    assert torch.equal(a[:1000], normal_values(s, 1000, 0.0, 0.02))          # element i does not depend on n
+    assert abs(float(a.mean())) < 2e-4 and abs(float(a.std()) - 0.02) < 2e-4
+    assert 0.66 < float((a.abs() < 0.02).float().mean()) < 0.70              # one sigma holds about 68 %
+    assert not torch.equal(a[:1000], normal_values(tensor_seed(3, "model.layers.1.mlp.up_proj.weight"), 1000, 0.0, 0.02))
+    b = normal_values(s, 1000, 1.0, 0.1)
+    assert abs(float(b.mean()) - 1.0) < 0.02
+
+
+def test_random_weights_without_a_folder_equal_the_folders(tmp_path):
+    """``Engine.from_random`` without a work folder draws the tensors where the engine runs (here through
+    the stand-in kernel set) and gives the engine the same tensors as writing the folder and loading it."""
+    from kernel_refs import ReferenceKernels
+    from infurnace_b200.engine import Engine, EngineOptions, SamplingParams
+    cfg = config_from_dict(tiny.TINY["B"]["config"])
+    opts = dict(dtype="float32", device="cpu", page_size=8, num_pages=32, max_num_seqs=2, max_num_batched_tokens=64)
+    a = Engine.from_random(cfg, 4, EngineOptions(**opts), kernels=ReferenceKernels())
+    b = Engine.from_random(cfg, 4, EngineOptions(**opts), kernels=ReferenceKernels(), workdir=str(tmp_path / "m"))
+    prompt = tiny.random_tokens(320, 12, 1)
+    assert a.generate([prompt], SamplingParams(max_tokens=8)) == b.generate([prompt], SamplingParams(max_tokens=8))
+    la, lb = a.runner.model.layers[1], b.runner.model.layers[1]
+    assert torch.equal(la.mixer.w_qkv, lb.mixer.w_qkv) and torch.equal(la.ffn.w_down, lb.ffn.w_down)
+    assert torch.equal(a.runner.model.lm_head.weight, b.runner.model.lm_head.weight)
