@@ -14,8 +14,10 @@ group has a page pool and, for each request, a block table of its own, because i
 pages come and go by its own rule: a full-attention group holds a request's pages
 until the request ends, a window group gives a page back as soon as every key in it
 lies below the window of the request's next query.  Each cache entry (one per layer
-call that stores) of a group has a tensor ``[pages, 2, kv_heads, page_size, head_dim]``;
-the entries of one group share page ids, so one block table serves them all.
+call that stores) of a group has a tensor ``[pages, 2, kv_heads, page_size, head_dim]``
+(keys and values of one shape), or, for a need whose streams differ in shape (values narrower
+than keys, a latent beside a small rotated key), one tensor ``[pages, heads, page_size, width]``
+per stream; the entries of one group share page ids, so one block table serves them all.
 
 State slots.  A request gets a slot id when it is added and returns it when it ends.
 The id is the row of the request in every fixed-size state tensor ``[slots, *shape]``
@@ -31,7 +33,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
-from ..config.specs import KVCacheNeed, ModelPlan, StateNeed
+from ..config.specs import KVCacheNeed, ModelPlan, PagedCacheNeed, StateNeed
 from ..errors import CacheError, OutOfPages
 from .block_pool import BlockPool
 
@@ -45,7 +47,14 @@ class KVGroup:
     pool: BlockPool
     page_size: int
     tables: Dict[str, List[int]] = field(default_factory=dict)
-    tensors: Dict[int, object] = field(default_factory=dict)      # cache id -> device tensor
+    tensors: Dict[int, object] = field(default_factory=dict)      # cache id -> device tensor (None: streams of unequal shape)
+    streams: Dict[int, Dict[str, object]] = field(default_factory=dict)      # cache id -> stream name -> device tensor
+
+    @property
+    def uniform(self) -> bool:
+        """All streams have one shape, so an entry is a single tensor with a stream axis."""
+        st = self.need.streams
+        return all((x.heads, x.width) == (st[0].heads, st[0].width) for x in st)
 
     def first_needed_page(self, next_position: int) -> int:
         """Index of the first logical page that the query at ``next_position`` can read."""
@@ -79,7 +88,7 @@ class CacheLayout:
                                      f"({key}) than the layer that stores it ({self.group_of[call.cache]})")
                 continue
             self.group_of[call.cache] = key
-            table = self.kv if isinstance(need, KVCacheNeed) else self.state
+            table = self.kv if isinstance(need, (KVCacheNeed, PagedCacheNeed)) else self.state
             table.setdefault(key, (need, []))[1].append(call.cache)
 
 
@@ -118,10 +127,17 @@ class CacheManager:
         if allocate_tensors:
             import torch
             for g in self.kv_groups:
+                st = g.need.streams
                 for cid in g.cache_ids:
-                    g.tensors[cid] = torch.zeros(
-                        (g.pool.num_pages, 2, g.need.num_kv_heads, page_size, g.need.head_dim),
-                        dtype=dtype, device=device)
+                    if g.uniform:
+                        t = torch.zeros((g.pool.num_pages, len(st), st[0].heads, page_size, st[0].width),
+                                        dtype=dtype, device=device)
+                        g.tensors[cid] = t
+                        g.streams[cid] = {x.name: t[:, i] for i, x in enumerate(st)}
+                    else:
+                        g.tensors[cid] = None
+                        g.streams[cid] = {x.name: torch.zeros((g.pool.num_pages, x.heads, page_size, x.width),
+                                                              dtype=dtype, device=device) for x in st}
             for g in self.state_groups:
                 for cid in g.cache_ids:
                     g.tensors[cid] = torch.zeros((max_requests, *g.need.shape), dtype=torch.float32, device=device)
@@ -165,8 +181,9 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         total = 0
         for g in self.kv_groups:
-            for t in g.tensors.values():
-                total += 2 * g.need.num_kv_heads * g.need.head_dim * t.element_size()
+            for streams in g.streams.values():
+                for x in g.need.streams:
+                    total += x.heads * x.width * streams[x.name].element_size()
         return total
 
     # ------------------------------------------------------------------ life of a request

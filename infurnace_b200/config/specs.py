@@ -35,19 +35,49 @@ class TensorSpec:
 
 # --------------------------------------------------------------------------- cache needs
 @dataclass(frozen=True)
+class PagedStream:
+    """One thing a mixer keeps per token in the pages: ``heads`` rows of ``width`` elements."""
+    name: str
+    heads: int
+    width: int
+
+
+@dataclass(frozen=True)
 class KVCacheNeed:
     """Keys and values that grow with the sequence, kept in pages.
 
     ``window`` None: every earlier key stays visible.  ``window`` w: a query at
     position p sees keys at positions p-w+1 .. p, and pages that lie wholly below
-    that range are given back while the request still runs."""
+    that range are given back while the request still runs.  ``value_head_dim``: the
+    width of a value head where it differs from a key head's."""
     num_kv_heads: int
     head_dim: int
+    window: Optional[int] = None
+    value_head_dim: Optional[int] = None
+
+    @property
+    def streams(self) -> Tuple[PagedStream, ...]:
+        return (PagedStream("k", self.num_kv_heads, self.head_dim),
+                PagedStream("v", self.num_kv_heads, self.value_head_dim or self.head_dim))
+
+    @property
+    def group_key(self):
+        return ("kv", self.streams, self.window)
+
+
+@dataclass(frozen=True)
+class PagedCacheNeed:
+    """Per-token entries of any shape, kept in pages: a tuple of streams (a compressed latent and a
+    small rotated key, say, instead of full keys and values), with the same window rule as
+    :class:`KVCacheNeed`.  A cache entry then has one tensor per stream,
+    ``[pages, heads, page_size, width]``; streams of equal shape share one tensor
+    ``[pages, streams, heads, page_size, width]`` (which is the layout of keys and values)."""
+    streams: Tuple[PagedStream, ...]
     window: Optional[int] = None
 
     @property
     def group_key(self):
-        return ("kv", self.num_kv_heads, self.head_dim, self.window)
+        return ("kv", self.streams, self.window)
 
 
 @dataclass(frozen=True)

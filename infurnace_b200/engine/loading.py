@@ -76,7 +76,7 @@ def default_num_pages(plan, options, dtype, device, max_len) -> int:
     per_page = 0
     esize = torch.empty((), dtype=dtype).element_size()
     for need, ids in layout.kv.values():
-        per_page += len(ids) * 2 * need.num_kv_heads * need.head_dim * options.page_size * esize
+        per_page += len(ids) * sum(x.heads * x.width for x in need.streams) * options.page_size * esize
     want = options.max_num_seqs * (-(-max_len // options.page_size)) + 1
     if per_page == 0:
         return 1

@@ -58,12 +58,15 @@ class SampledTokens:
 
 @dataclass
 class KVView:
-    """What a mixer gets for its cache entry: the entry's pages and its group's tables."""
-    pages: torch.Tensor
+    """What a mixer gets for its cache entry: the entry's pages and its group's tables.  ``pages`` is the
+    entry's one tensor ``[pages, streams, heads, page_size, width]`` when all its streams have one shape
+    (keys and values), else None; ``streams`` has each stream's ``[pages, heads, page_size, width]`` by name."""
+    pages: Optional[torch.Tensor]
     block_tables: torch.Tensor
     slot_mapping: torch.Tensor
     page_size: int
     window: Optional[int]
+    streams: Optional[Dict[str, torch.Tensor]] = None
 
 
 class _Arena:
@@ -116,7 +119,7 @@ class StepContext:
         gi = cache.kv_group_of(cache_id)
         g = cache.kv_groups[gi]
         return KVView(g.tensors[cache_id], self.group_block_tables[gi], self.group_slot_mapping[gi],
-                      g.page_size, g.need.window)
+                      g.page_size, g.need.window, g.streams.get(cache_id))
 
     def state(self, cache_id: int) -> torch.Tensor:
         """The fixed-size state tensor ``[slots, *shape]`` of a cache entry; request r of this

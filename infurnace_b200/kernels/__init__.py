@@ -2,6 +2,8 @@
 it raises :class:`~infurnace_b200.errors.KernelError` when there is no CUDA device."""
 from __future__ import annotations
 
+from .build import load_library, register_library  # noqa: F401  (for parts that bring kernels of their own)
+
 _kernels = None
 
 

@@ -27,7 +27,7 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
-# library name -> (sources, extra flags)
+# library name -> (sources, extra flags); sources are file names under csrc, or absolute paths (register_library)
 LIBRARIES: Dict[str, tuple] = {
     "core": (["elementwise.cu", "linear_simt.cu", "attention_simt.cu", "linear_skinny.cu", "linear_gemv.cu"], []),
     "linear_tcgen05": (["linear_tcgen05.cu"], []),
@@ -41,6 +41,23 @@ LIBRARIES: Dict[str, tuple] = {
 # what the build check compiles beside "core": the head size of the Qwen3 checkpoints and those of
 # the tiny test models; any other multiple of 16 up to 256 is compiled when a model first needs it
 DEFAULT_VARIANTS = [("attention_mma", {"HEAD_DIM": d}) for d in (128, 16, 32, 48)]
+
+def register_library(name: str, sources: Sequence[str], flags: Sequence[str] = (), *, replace: bool = False) -> None:
+    """Make a library of CUDA sources from outside the package known to :func:`load_library`, so that a
+    part defined elsewhere brings its own kernels: ``sources`` are paths of ``.cu`` files (relative paths
+    are taken from the caller's working directory), which may include the package's headers (``common.cuh``)
+    by name.  The part then calls ``load_library(name)``, declares the argument types of its entry points on the
+    returned ``ctypes.CDLL`` and launches on ``torch.cuda.current_stream().cuda_stream``."""
+    if name in LIBRARIES and not replace:
+        raise KernelError(f"a kernel library named {name!r} is already registered")
+    paths = [os.path.abspath(s) for s in sources]
+    for p in paths:
+        if not os.path.exists(p):
+            raise KernelError(f"kernel source {p} does not exist")
+    LIBRARIES[name] = (paths, list(flags))
+    for key in [k for k in _loaded if k.startswith(name + "[")]:
+        del _loaded[key]
+
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -82,25 +99,35 @@ def build_dir() -> str:
         return _build_dir
 
 
+def _source_path(name: str, beside: Optional[str] = None) -> Optional[str]:
+    """Where a source or a quoted include is: an absolute path, a file beside the including file, or under csrc."""
+    for cand in ([name] if os.path.isabs(name) else
+                 ([os.path.join(os.path.dirname(beside), name)] if beside else []) + [os.path.join(CSRC, name)]):
+        if os.path.exists(cand):
+            return cand
+    return None
+
+
 def _closure(sources: Sequence[str]) -> List[str]:
-    """The sources and every file of csrc that they include with quotes, directly or not."""
+    """The paths of the sources and of every file that they include with quotes, directly or not."""
     import re
-    seen, todo = [], list(sources)
+    seen, todo = [], [(s, None) for s in sources]
     while todo:
-        name = todo.pop(0)
-        if name in seen or not os.path.exists(os.path.join(CSRC, name)):
+        name, beside = todo.pop(0)
+        path = _source_path(name, beside)
+        if path is None or path in seen:
             continue
-        seen.append(name)
-        with open(os.path.join(CSRC, name), "r", encoding="utf-8") as f:
-            todo.extend(re.findall(r'^\s*#\s*include\s*"([^"]+)"', f.read(), flags=re.M))
+        seen.append(path)
+        with open(path, "r", encoding="utf-8") as f:
+            todo.extend((inc, path) for inc in re.findall(r'^\s*#\s*include\s*"([^"]+)"', f.read(), flags=re.M))
     return seen
 
 
 def _hash(sources: Sequence[str], flags: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for name in _closure(sources):
-        with open(os.path.join(CSRC, name), "rb") as f:
-            h.update(name.encode() + b"\0" + f.read())
+    for path in _closure(sources):
+        with open(path, "rb") as f:
+            h.update(os.path.basename(path).encode() + b"\0" + f.read())
     h.update(" ".join(list(ARCH_FLAGS) + list(BASE_FLAGS) + list(flags)).encode())
     return h.hexdigest()[:16]
 
@@ -121,7 +148,7 @@ def compile_library(name: str, defines: Optional[Dict[str, object]] = None, prog
     flags = list(flags) + [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
     tmp = f"{path}.{os.getpid()}.tmp"
     cmd = [find_nvcc(), *ARCH_FLAGS, *BASE_FLAGS, *flags, "-I", CSRC, "-o", tmp,
-           *[os.path.join(CSRC, s) for s in sources]]
+           *[_source_path(s) or os.path.join(CSRC, s) for s in sources]]
     label = os.path.basename(path)
     _say(progress, f"compiling {label} ({len(sources)} source files) with nvcc ...")
     t0 = time.monotonic()
@@ -148,7 +175,7 @@ def compile_library(name: str, defines: Optional[Dict[str, object]] = None, prog
 
 
 def load_library(name: str, defines: Optional[Dict[str, object]] = None, progress=None) -> ctypes.CDLL:
-    key = name + repr(sorted((defines or {}).items()))
+    key = name + repr(sorted((defines or {}).items()))       # "name[...]"
     with _lock:
         lib = _loaded.get(key)
         if lib is None:

@@ -103,8 +103,8 @@ class ReferenceKernels:
         page * page_size + offset; -1: not stored).  kv_pages: [pages, 2, nkv, page_size, d]."""
         N = qkv.shape[0]
         nq, nkv, d = num_heads, num_kv_heads, head_dim
-        q = qkv[:, : nq * d].to(self.cd).view(N, nq, d)
-        k = qkv[:, nq * d: (nq + nkv) * d].to(self.cd).view(N, nkv, d)
+        q = qkv[:, : nq * d].to(self.cd).reshape(N, nq, d).clone()
+        k = qkv[:, nq * d: (nq + nkv) * d].to(self.cd).reshape(N, nkv, d).clone()
         v = qkv[:, (nq + nkv) * d:].view(N, nkv, d)
 
         def norm(t, w):
