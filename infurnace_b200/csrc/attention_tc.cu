@@ -404,10 +404,12 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         m_used = m_new;
       }
       const float ref = m_used == -INFINITY ? 0.f : m_used;
+      bool o_waited = false;                 // whether this step has waited for the previous half's P V
       if (u > 0 && any_grow) {
         // O is rescaled between the previous half's P V, which must have landed, and this half's, which waits for P
         ok = __all_sync(0xffffffffu, tc_mbar_wait(o_done, (u - 1) & 1, abort_flag, err, 16)) != 0;
         if (!ok) break;
+        o_waited = true;
         tc_fence_after();
         l *= factor;
 #pragma unroll 1
@@ -451,6 +453,15 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       l += (lc[0] + lc[1]) + (lc[2] + lc[3]);
       tc_wait_st();
       tc_fence_before();
+      // A wait by parity tells phase k of o_done from phase k - 2 only for a waiter that has seen phase k - 1.  Half u's
+      // scores imply that P V of half u - 2 has landed (the tensor core runs one warp's operations in order) but say
+      // nothing of half u - 1, so every step waits for it (by now it has almost always landed) before it hands over P:
+      // the step that skipped it when no row's maximum grew would leave the wait after the last half one phase short,
+      // and that wait would pass on the phase two back while P V was still in flight.
+      if (u > 0 && !o_waited) {
+        ok = __all_sync(0xffffffffu, tc_mbar_wait(o_done, (u - 1) & 1, abort_flag, err, 19)) != 0;
+        if (!ok) break;
+      }
       tc_mbar_arrive(&bars.p_ready[x][h]);
     }
     if (ok && n_mine > 0) {

@@ -505,6 +505,80 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, const
   if (tid == 0) out[row] = chosen;
 }
 
+// ------------------------------------------------------------------------------------------
+// argmax of every row with several blocks per row (greedy sampling of a large vocabulary: one block per row leaves
+// most of the device idle).  Block (b, row) scans slice b of the row and writes its (largest value, lowest index of
+// it); the block of a row that finishes last (a counter per row, which it sets back to zero) takes the best of the
+// slices, the lowest index among equals, so the result is the one of sample_kernel.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ part_val, int* __restrict__ part_idx,
+                   int* __restrict__ counters, int* __restrict__ out) {
+  __shared__ float best_val[8];
+  __shared__ int best_idx[8];
+  __shared__ int is_last;
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int row = blockIdx.y, b = blockIdx.x, bpr = gridDim.x, tid = threadIdx.x;
+  const float* l = logits + (size_t)row * vocab;
+  const int chunk = ((vocab + bpr - 1) / bpr + 3) & ~3;
+  const int begin = min(vocab, b * chunk), end = min(vocab, begin + chunk);
+  float bv = -INFINITY; int bi = 0;      // a slice without any comparable value (all NaN) gives index 0
+  auto take = [&](float v, int i) { if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } };
+  if ((((uintptr_t)l) & 15) == 0) {
+    const int v4 = (end - begin) >> 2;
+    const float4* l4 = reinterpret_cast<const float4*>(l + begin);
+#pragma unroll 4
+    for (int i = tid; i < v4; i += 256) {
+      const float4 v = l4[i];
+      const int at = begin + (i << 2);
+      take(v.x, at); take(v.y, at + 1); take(v.z, at + 2); take(v.w, at + 3);
+    }
+    for (int i = begin + (v4 << 2) + tid; i < end; i += 256) take(l[i], i);
+  } else {
+    for (int i = begin + tid; i < end; i += 256) take(l[i], i);
+  }
+  if (bv == -INFINITY && bi == 0) bi = begin < vocab ? begin : 0;     // nothing taken: stay inside the slice
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if ((tid & 31) == 0) { best_val[tid >> 5] = bv; best_idx[tid >> 5] = bi; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int wv = 1; wv < 8; ++wv)
+      if (best_val[wv] > bv || (best_val[wv] == bv && best_idx[wv] < bi)) { bv = best_val[wv]; bi = best_idx[wv]; }
+    part_val[(size_t)row * bpr + b] = bv;
+    part_idx[(size_t)row * bpr + b] = bi;
+    __threadfence();
+    is_last = atomicAdd(&counters[row], 1) == bpr - 1;
+  }
+  __syncthreads();
+  if (!is_last || tid >= 32) return;
+  __threadfence();
+  bv = -INFINITY; bi = 0x7fffffff;
+  for (int p = tid; p < bpr; p += 32) {
+    const float v = part_val[(size_t)row * bpr + p]; const int i = part_idx[(size_t)row * bpr + p];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (tid == 0) { out[row] = min(max(bi, 0), vocab - 1); counters[row] = 0; }
+}
+
+// scratch: blocks_per_row * rows floats and as many ints; counters: rows ints, zero before the first call (the kernel
+// leaves them zero).  blocks_per_row <= 1024.
+IFB_EXPORT int ifb_argmax_rows(const float* logits, int rows, int vocab, int blocks_per_row, float* part_val, int* part_idx,
+                               int* counters, int* out, cudaStream_t stream) {
+  if (rows <= 0) return IFB_OK;
+  if (vocab < 1 || blocks_per_row < 1 || blocks_per_row > 1024 || rows > 65535) return IFB_ERR_SIZE;
+  if (!part_val || !part_idx || !counters) return IFB_ERR_ARG;
+  return ifb_launch(argmax_rows_kernel, dim3(blocks_per_row, rows), dim3(256), 0, stream, logits, vocab, part_val, part_idx,
+                    counters, out);
+}
+
 IFB_EXPORT int ifb_sample(const float* logits, int rows, int vocab, const float* temperature, const float* uniform,
                           int* out, cudaStream_t stream) {
   if (rows <= 0) return IFB_OK;

@@ -73,9 +73,13 @@ class _Arena:
     """Named device buffers that keep their address from step to step."""
 
     def __init__(self, device, max_rows):
+        import os
         self.device, self.max_rows = device, max_rows
         self._bufs: Dict[tuple, torch.Tensor] = {}
         self.generation = 0          # bumped whenever a buffer is (re)allocated: captured graphs go stale
+        # a debugging aid: new buffers start as NaN (floating) or as a large negative number (integer), so that a
+        # kernel that reads what no kernel wrote shows in the logits instead of depending on what the memory held
+        self.poison = os.environ.get("INFURNACE_POISON_BUFFERS", "0") not in ("", "0")
 
     def get(self, name, shape, dtype, rows=None):
         cap = max(rows or self.max_rows, shape[0])
@@ -83,6 +87,8 @@ class _Arena:
         buf = self._bufs.get(key)
         if buf is None or buf.shape[0] < cap:
             buf = torch.empty((cap, *shape[1:]), dtype=dtype, device=self.device)
+            if self.poison:
+                buf.fill_(float("nan") if dtype.is_floating_point else -(1 << 30))
             self._bufs[key] = buf
             self.generation += 1
         return buf[: shape[0]]

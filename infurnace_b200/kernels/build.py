@@ -193,4 +193,13 @@ def build_all(progress=None) -> List[str]:
     from concurrent.futures import ThreadPoolExecutor
     jobs = [("core", None), ("linear_tcgen05", None), ("linear_skinny_static", None), ("attention_tc", None)] + DEFAULT_VARIANTS
     with ThreadPoolExecutor(max_workers=4) as pool:
-        return list(pool.map(lambda j: compile_library(j[0], j[1], progress), jobs))
+        built = list(pool.map(lambda j: compile_library(j[0], j[1], progress), jobs))
+    # objects of older sources are never loaded (their names carry another hash); take them out of the folder
+    keep = {os.path.basename(p) for p in built}
+    for name in os.listdir(build_dir()):
+        if name.startswith("libifb_") and name.endswith(".so") and name not in keep:
+            try:
+                os.remove(os.path.join(build_dir(), name))
+            except OSError:
+                pass
+    return built

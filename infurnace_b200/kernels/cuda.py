@@ -71,6 +71,8 @@ class CudaKernels:
                                              c_void_p]
         c.ifb_rope_table.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]
         c.ifb_sample.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+        c.ifb_argmax_rows.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+        self._argmax_scratch = None    # (values, indices, counters) of the several-blocks-per-row argmax
         c.ifb_linear_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_void_p]
         c.ifb_linear_skinny.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -79,6 +81,13 @@ class CudaKernels:
                                       c_float, c_int, c_void_p]
         c.ifb_linear_gemv_residual_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                     c_int, c_int, c_int, c_void_p]
+        c.ifb_linear_gemv_qkv.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                          c_float, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                                          c_int, c_void_p]
+        self.fused_qkv = os.environ.get("INFURNACE_FUSED_QKV", "1") != "0"
+        self.fused_qkv_calls = 0
+        c.ifb_linear_gemv_set_plan.argtypes = [c_int]
+        c.ifb_linear_gemv_set_plan.restype = None
         c.ifb_linear_skinny_scratch.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
         c.ifb_linear_skinny_scratch.restype = None
         self._lin_partials = None
@@ -176,12 +185,24 @@ class CudaKernels:
             return self._linear_gemv(x, w, out, n, o, k, epi, row_scale)
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 \
                 and out.dtype in (torch.bfloat16, torch.float32):
-            if n >= self.tc_min_rows:
+            if self._on_tcgen05(n, w):
                 return self._linear_tcgen05(x, w, out, n, o, k, epi)
-            return self._linear_gemv(x, w, out, n, o, k, epi)      # tc_min_rows - 1 <= gemv_max_rows
+            return self._linear_gemv(x, w, out, n, o, k, epi)
         self.launches += 1
         _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
                                          n, o, k, epi, self._stream()), "linear")
+
+    def _on_tcgen05(self, n, w):
+        """Which kernel a bfloat16 product of n rows against w runs on.  More than 64 rows: the tcgen05 kernel.
+        Up to 8 rows: the few-rows kernel.  Between, by measurement: the few-rows kernel re-reads the rows
+        from L2 in every CTA, so for a large weight matrix (from 2^24 elements, or from 33 rows and 4,096
+        features) the tcgen05 kernel, which streams the weights once through its tiles, is the faster one
+        although most of its 128-row tile is empty."""
+        if n >= self.tc_min_rows:
+            return True
+        if n <= 8:
+            return False
+        return w.numel() >= (1 << 24) or (n >= 33 and w.shape[0] >= 4096)
 
     def _linear_tcgen05(self, x, w, out, n, o, k, epi, shape=0):
         """shape: 0 lets the library choose its tile shape; 1 narrow, 2 deep, 3 wide."""
@@ -223,7 +244,7 @@ class CudaKernels:
         """Whether a product of ``n`` rows of ``dtype`` against ``w`` runs on the kernel that can
         take or make a folded norm."""
         return (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
-                and 0 < n <= min(self.gemv_max_rows, self.fold_max_rows))
+                and 0 < n <= min(self.gemv_max_rows, self.fold_max_rows) and not self._on_tcgen05(n, w))
 
     def fold_parts(self, out_features):
         """Partial sums per row that :meth:`linear_residual_norm` writes."""
@@ -274,6 +295,53 @@ class CudaKernels:
         self.launches += 1
         _check(self.core.ifb_linear_skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), _ptr(partials),
                                            _ptr(counters), n, o, k, epi, splits, self._stream()), "linear")
+
+    # The q | k | v projection of a decode step with the head norm, the rotation and the page store in its epilogue.
+    def can_fuse_qkv(self, n, dtype, w_qkv, head_dim, rotary_dim, interleaved, kv_pages):
+        """Whether :meth:`linear_qkv_rope_store` takes a step of ``n`` rows: few rows of bfloat16 on the few-rows
+        kernel, heads of 64, 128 or 256 rotated whole in the half-split pairing (or not rotated)."""
+        return (self.fused_qkv and 0 < n <= 16 and dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
+                and w_qkv.shape[1] % 8 == 0 and head_dim in (64, 128, 256) and not self._on_tcgen05(n, w_qkv)
+                and (rotary_dim == 0 or (rotary_dim == head_dim and not interleaved))
+                and (kv_pages is None or kv_pages.dtype == torch.bfloat16))
+
+    def linear_qkv_rope_store(self, x, w_qkv, qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, rope_table,
+                              slot_mapping, kv_pages, row_scale=None):
+        """qkv = x w_qkv^T, then per head what :meth:`qk_norm_rope_store` does (RMSNorm of the q and k heads,
+        rotation by the angles of ``rope_table``, k and v into the pages at ``slot_mapping``), in one launch."""
+        _dense(x, "x", torch.bfloat16), _dense(w_qkv, "w_qkv", torch.bfloat16), _dense(qkv, "qkv", torch.bfloat16)
+        n, k = x.shape
+        width = (num_heads + 2 * num_kv_heads) * head_dim
+        if w_qkv.shape != (width, k) or qkv.shape != (n, width):
+            raise KernelError("linear_qkv_rope_store: sizes of x, w_qkv and qkv do not match the heads")
+        wd = F32
+        for wt in (q_weight, k_weight):
+            if wt is not None:
+                _dense(wt, "norm weight")
+                if wt.numel() != head_dim:
+                    raise KernelError("linear_qkv_rope_store: norm weight length is not head_dim")
+                wd = _code(wt)
+        if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
+            raise KernelError("linear_qkv_rope_store: q and k norm weights differ in dtype")
+        if rope_table is not None:
+            _dense(rope_table, "rope_table", torch.float32)
+            if rope_table.shape != (n, head_dim):
+                raise KernelError("linear_qkv_rope_store: rope_table is [tokens, head_dim]")
+        page_size = 1
+        if slot_mapping is not None:
+            _dense(slot_mapping, "slot_mapping", torch.int32), _dense(kv_pages, "kv_pages", torch.bfloat16)
+            if kv_pages.dim() != 5 or kv_pages.shape[1] != 2 or kv_pages.shape[2] != num_kv_heads \
+                    or kv_pages.shape[4] != head_dim or slot_mapping.numel() != n:
+                raise KernelError("linear_qkv_rope_store: kv_pages is not [pages, 2, kv_heads, page_size, head_dim]")
+            page_size = kv_pages.shape[3]
+        partials, parts, seps, swidth = row_scale if row_scale is not None else (None, 0, 0.0, 0)
+        self.launches += 1
+        self.fused_qkv_calls += 1
+        _check(self.core.ifb_linear_gemv_qkv(
+            x.data_ptr(), w_qkv.data_ptr(), qkv.data_ptr(), n, num_heads, num_kv_heads, head_dim, k, _ptr(partials),
+            int(parts), float(seps), int(swidth), _ptr(q_weight), _ptr(k_weight), wd, float(eps), _ptr(rope_table),
+            _ptr(slot_mapping), _ptr(kv_pages) if slot_mapping is not None else 0, page_size, self._stream()),
+            "linear_qkv_rope_store")
 
     # ------------------------------------------------------------------ q/k norm, rotation, store
     def rope_table(self, positions, inv_freq, out):
@@ -442,5 +510,17 @@ class CudaKernels:
         if out.numel() != m:
             raise KernelError("sample: out has one entry per row")
         self.launches += 1
+        if temperature is None and vocab >= 16384 and m <= 4096:
+            # greedy over a large vocabulary: several blocks per row, enough to fill the device about twice
+            bpr = max(1, min(64, (2 * self.sm_count) // m, vocab // 2048))
+            if bpr > 1:
+                if self._argmax_scratch is None:
+                    self._argmax_scratch = (torch.empty(4096 * 64, dtype=torch.float32, device="cuda"),
+                                            torch.empty(4096 * 64, dtype=torch.int32, device="cuda"),
+                                            torch.zeros(4096, dtype=torch.int32, device="cuda"))
+                    self.scratch_generation += 1
+                vals, idxs, counters = self._argmax_scratch
+                return _check(self.core.ifb_argmax_rows(logits.data_ptr(), m, vocab, bpr, vals.data_ptr(), idxs.data_ptr(),
+                                                        counters.data_ptr(), out.data_ptr(), self._stream()), "sample")
         _check(self.core.ifb_sample(logits.data_ptr(), m, vocab, _ptr(temperature), _ptr(uniform), out.data_ptr(),
                                     self._stream()), "sample")

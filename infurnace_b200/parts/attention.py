@@ -47,13 +47,37 @@ class PagedAttention:
         h, row_scale = unfolded(h)
         n = h.shape[0]
         qkv = ctx.buffer("qkv", (n, self.qkv_width), self.rt.act_dtype)
-        if row_scale is not None:
-            k.linear(h, self.w_qkv, qkv, row_scale=row_scale)
-        else:
-            k.linear(h, self.w_qkv, qkv)
         kv = ctx.kv(call.cache)
         slots = kv.slot_mapping if call.store else None
         fused = self.position.fused_rotary() if self.position is not None else None
+        has_table = fused is not None and hasattr(self.position, "table")
+        one_launch = getattr(k, "can_fuse_qkv", None)
+        if (self.position is None or has_table) and one_launch and one_launch(
+                n, h.dtype, self.w_qkv, s.head_dim, fused[1] if fused is not None else 0,
+                bool(fused[2]) if fused is not None else False, kv.pages):
+            # few rows: the projection's own kernel finishes norm, rotation and store
+            k.linear_qkv_rope_store(h, self.w_qkv, qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm_w, self.k_norm_w,
+                                    self.eps, self.position.table(ctx) if fused is not None else None, slots, kv.pages,
+                                    row_scale=row_scale)
+        else:
+            if row_scale is not None:
+                k.linear(h, self.w_qkv, qkv, row_scale=row_scale)
+            else:
+                k.linear(h, self.w_qkv, qkv)
+            self._norm_rotate_store(qkv, ctx, kv, slots, fused)
+        attn = ctx.buffer("attn", (n, s.num_heads * s.head_dim), self.rt.act_dtype)
+        k.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, kv.pages, kv.block_tables,
+                          ctx.cu_q, ctx.seq_lens, attn, s.scale, s.window or 0, ctx.max_q_len, ctx.max_seq_len,
+                          min_q_len=ctx.min_q_len)
+        folded = fold_residual_norm(k, ctx, "mixer", attn, self.w_o, fold, self.rt.act_dtype)
+        if folded is not None:
+            return folded
+        delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
+        k.linear(attn, self.w_o, delta)
+        return delta
+
+    def _norm_rotate_store(self, qkv, ctx, kv, slots, fused):
+        s, k = self.spec, self.k
         if self.position is None or fused is not None:
             inv_freq, rdim, inter = fused if fused is not None else (None, 0, False)
             table = self.position.table(ctx) if fused is not None and hasattr(self.position, "table") else None
@@ -66,16 +90,6 @@ class PagedAttention:
             if slots is not None:
                 k.qk_norm_rope_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, None, None, 0.0,
                                      None, 0, False, ctx.positions, slots, kv.pages)
-        attn = ctx.buffer("attn", (n, s.num_heads * s.head_dim), self.rt.act_dtype)
-        k.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, kv.pages, kv.block_tables,
-                          ctx.cu_q, ctx.seq_lens, attn, s.scale, s.window or 0, ctx.max_q_len, ctx.max_seq_len,
-                          min_q_len=ctx.min_q_len)
-        folded = fold_residual_norm(k, ctx, "mixer", attn, self.w_o, fold, self.rt.act_dtype)
-        if folded is not None:
-            return folded
-        delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
-        k.linear(attn, self.w_o, delta)
-        return delta
 
 
 register_part(AttentionSpec, PagedAttention)

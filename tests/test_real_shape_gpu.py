@@ -115,7 +115,7 @@ def test_cutting_modes_at_the_real_head_size(small_06b, mode, dtype, tolerance):
     opts = EngineOptions(dtype=dtype, page_size=16, num_pages=1024 // 16, max_num_seqs=4, max_num_batched_tokens=1024)
     runner = build_runner(path, opts)[2]
     K = runner.rt.kernels
-    before = (K.tc_attention_calls, K.small_q_tma_calls)
+    before = (K.tc_attention_calls, K.small_q_tma_calls, K.fused_qkv_calls)
     out = tiny.collect(steps, tiny.run_inprocess(runner, steps), cfg["vocab_size"])
     runner.cache.check()
     assert runner.cache.free_pages() == [64]
@@ -135,6 +135,7 @@ def test_cutting_modes_at_the_real_head_size(small_06b, mode, dtype, tolerance):
         assert K.tc_attention_calls > before[0], "the tcgen05 attention kernel did not run"
         if mode != "whole":
             assert K.small_q_tma_calls > before[1], "the TMA-fed small-q kernel did not run"
+            assert K.fused_qkv_calls > before[2], "the q | k | v product with norm, rotation and store in its epilogue did not run"
     K.check_device_errors()
 
 
