@@ -257,6 +257,18 @@ class CacheManager:
             out.append(page * ps + pos % ps)
         return out
 
+    def slots_array(self, rid: str, group: int, num_new_tokens: int):
+        """``slots_for`` as an int32 numpy array, without a Python loop over the tokens."""
+        import numpy as np
+        g = self.kv_groups[group]
+        table, start, ps = g.tables[rid], self._computed[rid], self.page_size
+        pos = np.arange(start, start + num_new_tokens, dtype=np.int64)
+        first, last = start // ps, (start + num_new_tokens - 1) // ps
+        pages = np.asarray(table[first:last + 1], dtype=np.int64)
+        if (pages == RELEASED).any():
+            raise CacheError(f"request {rid!r} would store in a page it gave back")
+        return (pages[pos // ps - first] * ps + pos % ps).astype(np.int32)
+
     def commit(self, rid: str, num_new_tokens: int) -> None:
         """``num_new_tokens`` were stored.  Pages that every later query's window has passed
         go back to their pool; their block-table entries become ``RELEASED``."""

@@ -201,18 +201,31 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   // stores this step's keys, and its own successor, which waits for this grid alone, would then start too early
   if (q_len * G <= 16) { ifb_pdl_wait(); return; }           // the small-q kernel's request
   const int tpt = ROWS / G;                                  // tokens per query tile; a CTA takes two tiles
-  const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * 2 * tpt;   // longest key ranges first
-  if (t0 >= q_len) { ifb_pdl_wait(); return; }
-  const int t1 = min(q_len, t0 + 2 * tpt);
+  // Which two.  A tile's work grows with the keys it sees, so under the causal rule alone the CTA takes the j-th tile
+  // from the front and the j-th from the back of the request's tokens: every CTA then has the same work (the keys of
+  // the early tile are a prefix of the late tile's, so they still share them), where neighbouring tiles would give the
+  // last CTA twice the average.  With a window every tile sees about as many keys, and neighbours share the most.
+  const int nt = (q_len + tpt - 1) / tpt;
+  int tok0[2];                                               // first token of each tile; tile 1 absent: q_len
+  if (window > 0) {
+    tok0[0] = (int)(gridDim.x - 1 - blockIdx.x) * 2 * tpt;   // longest key ranges first
+    tok0[1] = min(q_len, tok0[0] + tpt);
+  } else {
+    const int j = blockIdx.x, other = nt - 1 - j;
+    tok0[0] = j <= other ? j * tpt : q_len;
+    tok0[1] = other > j ? other * tpt : q_len;
+  }
+  if (tok0[0] >= q_len) { ifb_pdl_wait(); return; }
   const int p_first = L - q_len;
-  const int lo = window > 0 ? max(0, p_first + t0 - window + 1) : 0, hi = p_first + t1 - 1;
+  const int t_end = tok0[1] < q_len ? min(q_len, tok0[1] + tpt) : min(q_len, tok0[0] + tpt);    // one past the CTA's last token
+  const int lo = window > 0 ? max(0, p_first + tok0[0] - window + 1) : 0, hi = p_first + t_end - 1;
   const int T0 = (lo / BK) * BK;
   // Keys are loaded in tiles of 128 and worked on in halves of 64: n_x[x] halves for query tile x (the second tile's
   // tokens come later, it sees at least as far).
   int n_x[2];
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
-    const int t0x = t0 + x * tpt;
+    const int t0x = tok0[x];
     const int hix = p_first + min(q_len, t0x + tpt) - 1;
     n_x[x] = (t0x < q_len && hix >= T0) ? (hix + 1 - T0 + SUB - 1) / SUB : 0;
   }
@@ -256,8 +269,8 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #pragma unroll
       for (int x = 0; x < 2; ++x)
         if (n_x[x] > 0 || x == 0) {
-          tc_tma_3d(Qs + x * TILE_BYTES, &q_map, &bars.q_full, 0, kvh * G, q0 + t0 + x * tpt);
-          tc_tma_3d(Qs + x * TILE_BYTES + HALF_BYTES, &q_map, &bars.q_full, 64, kvh * G, q0 + t0 + x * tpt);
+          tc_tma_3d(Qs + x * TILE_BYTES, &q_map, &bars.q_full, 0, kvh * G, q0 + tok0[x]);
+          tc_tma_3d(Qs + x * TILE_BYTES + HALF_BYTES, &q_map, &bars.q_full, 64, kvh * G, q0 + tok0[x]);
         }
     }
     const int ppt = BK >> ps_shift;                          // pages per tile: 8, 4 or 2
@@ -349,7 +362,7 @@ attn_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     const int x = (warp - 4) >> 2;
     const int qd = warp & 3;                                 // this warp's quarter of the 128 lanes
     const int row = qd * 32 + lane;
-    const int t0x = t0 + x * tpt, t1x = min(q_len, t0x + tpt);
+    const int t0x = tok0[x], t1x = min(q_len, t0x + tpt);
     const int tok = t0x + row / G;
     const int p = tok < t1x ? p_first + tok : NO_ROW;
     const int row_lo = window > 0 ? p - window + 1 : 0;

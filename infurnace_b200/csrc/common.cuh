@@ -62,8 +62,12 @@ static inline bool ifb_pdl_enabled() {
     }                                                                                                                   \
   } while (0)
 
+// early: whether this launch may be scheduled before its predecessor has finished.  A kernel that lives on its bytes in
+// flight is better off without: launched early, its CTAs sit on registers and shared memory of SMs where the
+// predecessor still has CTAs to place, and at these sizes the launch latency that the overlap hides is small change.
 template <typename... KArgs, typename... Args>
-static inline int ifb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+static inline int ifb_launch_opt(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -73,10 +77,15 @@ static inline int ifb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = ifb_pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = (early && ifb_pdl_enabled()) ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
   if (e != cudaSuccess) { cudaGetLastError(); return -(int)e; }
   return IFB_OK;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int ifb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  return ifb_launch_opt(true, kernel, grid, block, smem, stream, args...);
 }
 
 // ---------------------------------------------------------------------------------------------

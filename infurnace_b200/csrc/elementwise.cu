@@ -374,6 +374,89 @@ qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv
   }
 }
 
+// The same for bfloat16 heads of 128 and steps of many tokens, where the bytes count: a warp takes one token, half a warp
+// one head at a time with 16 bytes (8 elements) per lane, so a token's 32 heads are 16 passes of which eight are
+// requested at once; the rotation partner of an element sits 8 lanes on.
+__global__ void __launch_bounds__(128)
+qk_norm_rope_store_d128_kernel(__nv_bfloat16* __restrict__ qkv, int n_tokens, int nq, int nkv, const void* __restrict__ qw,
+                               const void* __restrict__ kw, int w_dtype, float eps, const float* __restrict__ rope_table,
+                               const int* __restrict__ slots, __nv_bfloat16* __restrict__ pages, int page_size) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  constexpr int d = 128, B = 8;                                // B passes (two heads each) in flight
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane >> 4, l16 = lane & 15;
+  const int tok = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (tok >= n_tokens) return;
+  const int heads = nq + 2 * nkv;
+  const int slot = slots ? slots[tok] : -1;
+  float cs[8], sn[8];                                          // the angles of elements l16 * 8 .. + 7 of the first half
+  if (rope_table) {
+    const float2* t = reinterpret_cast<const float2*>(rope_table) + (size_t)tok * (d / 2) + (l16 & 7) * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { cs[e] = t[e].x; sn[e] = t[e].y; }
+  }
+  float wq[8], wk[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    wq[e] = qw ? load_as_f32(qw, w_dtype, l16 * 8 + e) : 1.f;
+    wk[e] = kw ? load_as_f32(kw, w_dtype, l16 * 8 + e) : 1.f;
+  }
+  size_t page_base = 0;
+  if (slot >= 0) page_base = (size_t)(slot / page_size) * 2 * nkv * page_size + (slot % page_size);
+  __nv_bfloat16* row = qkv + (size_t)tok * heads * d;
+  for (int h0 = 0; h0 < heads; h0 += 2 * B) {
+    uint4 in[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const int head = h0 + 2 * b + sub;
+      in[b] = head < heads ? *reinterpret_cast<const uint4*>(row + (size_t)head * d + l16 * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const int head = h0 + 2 * b + sub;
+      const bool live = head < heads;
+      const bool is_v = head >= nq + nkv, is_k = head >= nq && !is_v;
+      __nv_bfloat16* dst = nullptr;
+      if (live && slot >= 0 && head >= nq)                    // pages[page][k or v][kv head][place][d]
+        dst = pages + (page_base + (size_t)(is_v ? nkv + head - nq - nkv : head - nq) * page_size) * d + l16 * 8;
+      const bool has_w = live && !is_v && (is_k ? kw != nullptr : qw != nullptr);
+      const bool rotate = live && !is_v && rope_table != nullptr;
+      float v[8];
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&in[b]);
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[2 * e] = __low2float(p2[e]); v[2 * e + 1] = __high2float(p2[e]);
+        ss += v[2 * e] * v[2 * e] + v[2 * e + 1] * v[2 * e + 1];
+      }
+      // the sum over the head's 16 lanes (both halves of the warp do this together, each for its own head)
+      ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      if (has_w) {
+        const float r = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = v[e] * r * (is_k ? wk[e] : wq[e]);
+      }
+      const bool first = l16 < 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float o = __shfl_xor_sync(0xffffffffu, v[e], 8);
+        if (rotate) v[e] = first ? v[e] * cs[e] - o * sn[e] : v[e] * cs[e] + o * sn[e];
+      }
+      uint4 res = in[b];
+      if (has_w || rotate) {
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) r2[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+        *reinterpret_cast<uint4*>(row + (size_t)head * d + l16 * 8) = res;
+      }
+      if (dst) *reinterpret_cast<uint4*>(dst) = res;
+    }
+  }
+}
+
 template <typename T>
 static int qk_vec_launch(int epl, unsigned blocks, cudaStream_t stream, T* qkv, int n_tokens, int nq, int nkv, const void* qw,
                          const void* kw, int w_dtype, float eps, const float* inv_freq, const float* rope_table,
@@ -400,6 +483,11 @@ IFB_EXPORT int ifb_qk_norm_rope_store(void* qkv, int dtype, int n_tokens, int nq
   const int warps = 4;
   const long long items = (long long)n_tokens * (nq + 2 * nkv);
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+  if (d == 128 && dtype == IFB_BF16 && n_tokens >= 64 && (!inv_freq || (rotary_dim == d && !interleaved && rope_table)) &&
+      ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)pages & 15) == 0)
+    return ifb_launch(qk_norm_rope_store_d128_kernel, dim3((unsigned)((n_tokens + warps - 1) / warps)), dim3(warps * 32), 0, stream,
+                      (__nv_bfloat16*)qkv, n_tokens, nq, nkv, qw, kw, w_dtype, eps, inv_freq ? rope_table : nullptr, slots,
+                      (__nv_bfloat16*)pages, page_size);
   if ((d == 64 || d == 128 || d == 256) && (!inv_freq || (rotary_dim == d && !interleaved)) &&
       (dtype == IFB_F32 || dtype == IFB_BF16) && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)pages & 15) == 0) {
     const long long vitems = (long long)n_tokens * ((nq + 2 * nkv + QK_HPW - 1) / QK_HPW);

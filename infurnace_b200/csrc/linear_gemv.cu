@@ -15,6 +15,7 @@
 
 typedef __nv_bfloat16 bf16;
 constexpr int GV_ROWS = 16;
+constexpr size_t GV_EARLY_BYTES = 24u << 20;     // weight bytes up to which a launch may start before its predecessor ends
 
 __device__ __forceinline__ uint4 gv_ld_stream16(const void* p) {
   uint4 v;
@@ -356,8 +357,10 @@ static int gv_launch(const void* x, const void* w, void* out, int n, int o, int 
   const size_t smem = ((size_t)WARPS * (EPI == 1 ? 2 : 1) * NB * 8 * GV_ROWS + NB * 8) * sizeof(float);
   IFB_ALLOW_SMEM((linear_gemv_kernel<NB, EPI, WARPS, TO, STAGES>), smem);
   dim3 grid((o + GV_ROWS - 1) / GV_ROWS, (n + NB * 8 - 1) / (NB * 8));
-  return ifb_launch(linear_gemv_kernel<NB, EPI, WARPS, TO, STAGES>, grid, dim3(WARPS * 32), smem, s, (const bf16*)x, (const bf16*)w,
-                    (TO*)out, n, o, k, rs, res, GvQkv{});
+  // matrices beyond GV_EARLY_BYTES are streamed; a launch ahead of the predecessor's end costs them more than it hides
+  const bool early = (size_t)o * k * (EPI == 1 ? 4 : 2) <= GV_EARLY_BYTES;
+  return ifb_launch_opt(early, linear_gemv_kernel<NB, EPI, WARPS, TO, STAGES>, grid, dim3(WARPS * 32), smem, s, (const bf16*)x,
+                        (const bf16*)w, (TO*)out, n, o, k, rs, res, GvQkv{});
 }
 
 // The fused q | k | v product: one CTA per (head, 16 feature pairs), the CTAs of a head as a thread-block cluster.
@@ -380,7 +383,7 @@ static int gv_launch_qkv(const void* x, const void* w, void* out, int n, int k, 
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = ifb_pdl_enabled() ? 2 : 1;
+  cfg.numAttrs = (ifb_pdl_enabled() && (size_t)heads * qk.head_dim * k * 2 <= GV_EARLY_BYTES) ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, linear_gemv_kernel<NB, 3, WARPS, bf16, STAGES>, (const bf16*)x, (const bf16*)w, (bf16*)out, n,
                                      heads * qk.head_dim, k, rs, GvResidual{nullptr, nullptr, 0, nullptr}, qk);
   if (e != cudaSuccess) { cudaGetLastError(); return -(int)e; }

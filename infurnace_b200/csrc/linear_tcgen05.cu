@@ -318,6 +318,236 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int k, int box_ro
   return ifb_tensor_map_bf16(m, ptr, 2, dims, strides, box);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The persistent form.  A CTA per SM walks a list of output tiles (tile t of the list goes to CTA t mod grid), with two
+// accumulators in tensor memory: while the epilogue warps read and store tile i from one, the issuer already
+// multiplies tile i + 1 into the other, and the producer's ring of stages never drains between tiles.  Tiles are
+// 128 tokens x NACC accumulator columns (128 or 256; with the silu_gate epilogue 128 gate + 128 up columns give 128
+// features); consecutive tiles of the list share their w tile, so it is read from L2 by the CTAs of one round.
+// The epilogue has its own staging rows in shared memory (the stages are busy with the next tile).
+// ---------------------------------------------------------------------------------------------------
+template <int EPI_, int NACC_, int STAGES_> struct PersistCfg {
+  static constexpr int EPI = EPI_, NACC = NACC_, STAGES = STAGES_;
+  static constexpr int FO = EPI ? NACC / 2 : NACC;            // output features per tile
+  static constexpr int A_BYTES = G_TILE_BYTES;                // 128 x rows of a stage
+  static constexpr int B_BYTES = NACC * G_BK * 2;             // w rows of a stage
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * NACC;                  // two accumulators: 256 or 512 columns
+  static constexpr int STAGING_PITCH = 128 + 16;              // a row segment of 128 bytes, padded against bank conflicts
+  static constexpr int STAGING_BYTES = 8 * 32 * STAGING_PITCH;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+  static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NACC >> 3) << 17) | ((uint32_t)(G_BM >> 4) << 24);
+};
+
+template <typename Cfg, typename TO>
+__global__ void __launch_bounds__(G_THREADS, 1)
+linear_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                                 TO* __restrict__ out, int n_rows, int o_out, int k_dim, int tiles_m, int tiles_total,
+                                 int* __restrict__ err) {
+  constexpr int EPI = Cfg::EPI, NACC = Cfg::NACC, FO = Cfg::FO, STAGES = Cfg::STAGES;
+  extern __shared__ unsigned char g_smem_raw[];
+  const uint32_t raw = g_smem_u32(g_smem_raw);
+  unsigned char* smem = g_smem_raw + (((raw + 1023u) & ~1023u) - raw);      // tiles need 1024-byte alignment
+  unsigned char* staging = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + Cfg::STAGING_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;                         // [2]: the issuer has finished a tile in accumulator b
+  uint64_t* acc_empty = acc_full + 2;                          // [2]: the eight epilogue warps have read accumulator b
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;     // warp-uniform
+  const int kblocks = (k_dim + G_BK - 1) / G_BK;
+  // this CTA's tiles: first, first + gridDim.x, ...; tile t covers tokens (t % tiles_m) * 128 and features (t / tiles_m) * FO
+  const int first = blockIdx.x, step = gridDim.x;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- producer.  The w tiles of the first stages, which no kernel of the step writes, are requested before this
+    // kernel waits for its predecessor in the stream; every x tile after.  (The other warps act only on what these
+    // loads bring, so the wait of this warp orders the whole CTA behind the predecessor.)
+    int g = 0;                                                  // k blocks issued so far, over all tiles
+    bool waited = false, ok = true;
+    for (int t = first; t < tiles_total && ok; t += step) {
+      const int m0 = (t % tiles_m) * G_BM, n0 = (t / tiles_m) * FO;
+      for (int kb = 0; kb < kblocks; ++kb, ++g) {
+        const int s = g % STAGES;
+        if (g >= STAGES && !mbar_wait(&empty[s], ((g / STAGES) - 1) & 1, abort_flag, err, 1)) { ok = false; break; }
+        unsigned char* stage = smem + s * Cfg::STAGE_BYTES;
+        if (elect_one()) {
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[s], kb * G_BK, n0);
+          if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[s], kb * G_BK, o_out + n0);
+        }
+        __syncwarp();
+        if (!waited && (g == STAGES - 1 || (kb == kblocks - 1 && t + step >= tiles_total))) {
+          // the ring is full of w tiles (or there are no more): now the predecessor, then the x tiles held back
+          ifb_pdl_wait();
+          ifb_pdl_trigger();
+          waited = true;
+          if (elect_one()) {
+            int gg = 0;
+            for (int tt = first; tt < tiles_total && gg <= g; tt += step)
+              for (int kk = 0; kk < kblocks && gg <= g; ++kk, ++gg)
+                tma_load_2d(smem + (gg % STAGES) * Cfg::STAGE_BYTES, &tmap_x, &full[gg % STAGES], kk * G_BK, (tt % tiles_m) * G_BM);
+          }
+          __syncwarp();
+        } else if (waited) {
+          if (elect_one()) tma_load_2d(stage, &tmap_x, &full[s], kb * G_BK, m0);
+          __syncwarp();
+        }
+      }
+    }
+    if (!waited) { ifb_pdl_wait(); ifb_pdl_trigger(); }         // a CTA without tiles still orders itself behind the predecessor
+  } else if (warp == 1) {
+    // ---- issuer: tile i of this CTA accumulates in accumulator i & 1
+    int g = 0, it = 0;
+    bool ok = true;
+    for (int t = first; t < tiles_total && ok; t += step, ++it) {
+      const int b = it & 1;
+      if (it >= 2) ok = mbar_wait(&acc_empty[b], ((it >> 1) - 1) & 1, abort_flag, err, 4);
+      if (!ok) break;
+      tc_fence_after();
+      for (int kb = 0; kb < kblocks && ok; ++kb, ++g) {
+        const int s = g % STAGES;
+        ok = mbar_wait(&full[s], (g / STAGES) & 1, abort_flag, err, 2);
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
+          const uint32_t a_addr = g_smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint64_t a_desc = make_smem_desc(a_addr);
+          const uint64_t b_desc = make_smem_desc(a_addr + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < G_BK / G_UK; ++k) {
+            const uint64_t kstep = (uint64_t)((k * G_UK * 2) >> 4);          // 32 bytes per k step, in 16-byte units
+            umma_bf16(tmem_base + b * NACC, a_desc + kstep, b_desc + kstep, Cfg::IDESC, (kb | k) != 0);
+          }
+          umma_commit(&empty[s]);
+          if (kb == kblocks - 1) umma_commit(&acc_full[b]);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ---- epilogue.  A warp's piece of a tile is 32 tokens (its lanes) by CW features, taken 128 bytes of a row at a
+    // time: from tensor memory to registers, to the warp's staging rows, and from there in whole row segments to `out`.
+    constexpr int CW = FO / 2;
+    constexpr int PW = 128 / (int)sizeof(TO);                    // features per staged row segment
+    constexpr int PITCH = Cfg::STAGING_PITCH;
+    static_assert(CW % PW == 0, "a warp's features are whole row segments");
+    const int q = warp & 3;                                      // this warp's quarter of the 128 lanes
+    const int c_lo = ((warp - 2) >> 2) * CW;                     // and its half of the tile's features
+    unsigned char* buf = staging + (warp - 2) * (32 * PITCH);
+    int it = 0;
+    bool ok = true;
+    for (int t = first; t < tiles_total && ok; t += step, ++it) {
+      const int b = it & 1;
+      const int m0 = (t % tiles_m) * G_BM, n0 = (t / tiles_m) * FO;
+      ok = mbar_wait(&acc_full[b], (it >> 1) & 1, abort_flag, err, 3);
+      if (!ok) break;
+      tc_fence_after();
+      const bool vec = ((size_t)o_out * sizeof(TO)) % 16 == 0 && (((uintptr_t)out) & 15) == 0 && n0 + c_lo + CW <= o_out;
+      const int row0 = m0 + q * 32;
+      const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + b * NACC;
+#pragma unroll 1
+      for (int p0 = c_lo; p0 < c_lo + CW; p0 += PW) {
+        if (n0 + p0 >= o_out) break;                             // warp-uniform
+#pragma unroll
+        for (int c0 = p0; c0 < p0 + PW; c0 += 32) {
+          uint32_t v[32];
+          float y[32];
+          tmem_ld32(lane_base + c0, v);
+          if (EPI) {
+            uint32_t u[32];
+            tmem_ld32(lane_base + FO + c0, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float gte = __uint_as_float(v[j]);
+              y[j] = gte * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * gte)) * __uint_as_float(u[j]);
+            }
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
+          }
+          if (vec) {
+            unsigned char* dst = buf + lane * PITCH + (c0 - p0) * (int)sizeof(TO);
+            if (sizeof(TO) == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(y[j], y[j + 1]), h1 = __floats2bfloat162_rn(y[j + 2], y[j + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(y[j + 4], y[j + 5]), h3 = __floats2bfloat162_rn(y[j + 6], y[j + 7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(dst + j * 2) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j * 4) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+            }
+          } else if (row0 + lane < n_rows) {
+            TO* dst = out + (size_t)(row0 + lane) * o_out + n0 + c0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c0 + j < o_out) dst[j] = from_f32<TO>(y[j]);
+          }
+        }
+        if (vec) {
+          __syncwarp();
+          unsigned char* obase = reinterpret_cast<unsigned char*>(out + (size_t)row0 * o_out + n0 + p0);
+#pragma unroll
+          for (int off = lane * 16; off < 32 * 128; off += 512) {
+            const int r = off >> 7, cb = off & 127;
+            if (row0 + r < n_rows)
+              *reinterpret_cast<uint4*>(obase + (size_t)r * o_out * sizeof(TO) + cb) = *reinterpret_cast<const uint4*>(buf + r * PITCH + cb);
+          }
+          __syncwarp();                                          // before the next segment overwrites the rows
+        }
+      }
+      // this warp has read its part of accumulator b: the issuer may overwrite it (with the tile after next)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(g_smem_u32(&acc_empty[b])) : "memory");
+    }
+  }
+  if (*abort_flag) {                         // a wait gave up: let copies in flight land before the CTA goes away
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, Cfg::TMEM_COLS); }
+}
+
+template <typename Cfg, typename TO>
+static int tc_launch_persistent(const void* x, const void* w, void* out, int n, int o, int k, int* err, int sm_count, cudaStream_t s) {
+  CUtensorMap mx, mw;
+  int st = make_map(&mx, x, n, k, G_BM);
+  if (st) return st;
+  st = make_map(&mw, w, Cfg::EPI ? 2 * o : o, k, Cfg::EPI ? Cfg::NACC / 2 : Cfg::NACC);
+  if (st) return st;
+  IFB_ALLOW_SMEM((linear_tcgen05_persistent_kernel<Cfg, TO>), Cfg::SMEM_BYTES);
+  const long long tiles_m = (n + G_BM - 1) / G_BM, tiles_n = (o + Cfg::FO - 1) / Cfg::FO;
+  if (tiles_m * tiles_n > 0x7fffffffLL) return IFB_ERR_SIZE;
+  const int total = (int)(tiles_m * tiles_n);
+  const int grid = total < sm_count ? total : sm_count;
+  return ifb_launch(linear_tcgen05_persistent_kernel<Cfg, TO>, dim3(grid), dim3(G_THREADS), (size_t)Cfg::SMEM_BYTES, s, mx, mw, (TO*)out, n,
+                    o, k, (int)tiles_m, total, err);
+}
+
 template <typename Cfg, typename TO>
 static int tc_launch_cfg(const void* x, const void* w, void* out, int n, int o, int k, int* err, cudaStream_t s) {
   CUtensorMap mx, mw;
@@ -332,8 +562,8 @@ static int tc_launch_cfg(const void* x, const void* w, void* out, int n, int o, 
 }
 
 // The shape of the tiles: a wave of wide tiles does four 128 x 128 products per SM in little more time than a wave of
-// narrow tiles (two CTAs per SM) does two, but only if there are enough wide tiles to fill the SMs.  shape: 0 chooses,
-// 1 narrow, 2 deep, 3 wide (for tests and measurements).
+// narrow tiles (two CTAs per SM) does two, but only if there are enough wide tiles to fill the SMs.  shape: 0 chooses
+// (see below), 1 narrow, 2 deep, 3 wide, 4 and 5 persistent (for tests and measurements).
 template <int EPI, typename TO>
 static int tc_launch(const void* x, const void* w, void* out, int n, int o, int k, int* err, int shape, cudaStream_t s) {
   static int sm_count = 0;
@@ -345,14 +575,25 @@ static int tc_launch(const void* x, const void* w, void* out, int n, int o, int 
   using Narrow = GemmCfg<EPI, 1, EPI ? 256 : 128, EPI ? 2 : 3>;
   using Deep = GemmCfg<EPI, 1, EPI ? 256 : 128, EPI ? 4 : 6>;
   using Wide = GemmCfg<EPI, 2, 256, 3>;
+  using P128 = PersistCfg<EPI, EPI ? 256 : 128, EPI ? 3 : 5>;      // 128 features per tile
+  using P256 = PersistCfg<EPI, 256, 3>;                            // 256 features per tile (plain epilogue only)
   if (shape == 0) {
-    const long long tn = (long long)((o + Narrow::FO - 1) / Narrow::FO) * ((n + G_BM - 1) / G_BM);
-    const long long tw = (long long)((o + Wide::FO - 1) / Wide::FO) * ((n + 2 * G_BM - 1) / (2 * G_BM));
-    const double cost_narrow = (double)((tn + 2 * sm_count - 1) / (2 * sm_count));
-    const double cost_wide = (double)((tw + sm_count - 1) / sm_count) * 1.15;
-    // (with the silu_gate epilogue a narrow tile already accumulates 256 columns per product, and measured faster)
-    shape = (!EPI && n > G_BM && cost_wide < cost_narrow) ? 3 : (tn <= sm_count ? 2 : 1);
+    // By measurement.  With the silu_gate epilogue: the persistent kernel (its tile already accumulates 256 columns per
+    // product, and the heavy epilogue of one tile runs beside the products of the next).  Otherwise one tile per CTA:
+    // the wide shape when there are enough wide tiles to fill the SMs (a 256 x 256 tile reads half the operand bytes
+    // per product from shared memory, which is what bounds these kernels), else the deep or the narrow one.
+    if (EPI) {
+      shape = 4;
+    } else {
+      const long long tn = (long long)((o + Narrow::FO - 1) / Narrow::FO) * ((n + G_BM - 1) / G_BM);
+      const long long tw = (long long)((o + Wide::FO - 1) / Wide::FO) * ((n + 2 * G_BM - 1) / (2 * G_BM));
+      const double cost_narrow = (double)((tn + 2 * sm_count - 1) / (2 * sm_count));
+      const double cost_wide = (double)((tw + sm_count - 1) / sm_count) * 1.15;
+      shape = (n > G_BM && cost_wide < cost_narrow) ? 3 : (tn <= sm_count ? 2 : 1);
+    }
   }
+  if (shape == 5 && !EPI) return tc_launch_persistent<P256, TO>(x, w, out, n, o, k, err, sm_count, s);
+  if (shape == 4 || shape == 5) return tc_launch_persistent<P128, TO>(x, w, out, n, o, k, err, sm_count, s);
   if (shape == 3) return tc_launch_cfg<Wide, TO>(x, w, out, n, o, k, err, s);
   if (shape == 2) return tc_launch_cfg<Deep, TO>(x, w, out, n, o, k, err, s);
   return tc_launch_cfg<Narrow, TO>(x, w, out, n, o, k, err, s);
@@ -360,14 +601,15 @@ static int tc_launch(const void* x, const void* w, void* out, int n, int o, int 
 
 // x [n_rows, k] and w [out_features (x2 for the silu_gate epilogue), k] bfloat16, 16-byte aligned, k a multiple of 8;
 // out bfloat16 or float32.  `err` points to a device int that stays 0 unless a bounded wait gave up.  shape: 0 lets the
-// library choose the tile shape, 1-3 force narrow, deep or wide.
+// library choose (the persistent kernel), 1-3 force the one-tile-per-CTA kernel narrow, deep or wide, 4 and 5 the
+// persistent kernel with tiles of 128 or 256 features.
 IFB_EXPORT int ifb_linear_tcgen05(const void* x, const void* w, void* out, int out_dtype, int n_rows, int out_features,
                                   int k_dim, int epilogue, int* err, int shape, cudaStream_t stream) {
   if (n_rows <= 0 || out_features <= 0) return IFB_OK;
   if (k_dim < 8 || k_dim % 8) return IFB_ERR_SIZE;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return IFB_ERR_ALIGN;
   if (epilogue != 0 && epilogue != 1) return IFB_ERR_ARG;
-  if (shape < 0 || shape > 3) return IFB_ERR_ARG;
+  if (shape < 0 || shape > 5) return IFB_ERR_ARG;
   if (out_dtype == IFB_BF16)
     return epilogue ? tc_launch<1, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, stream)
                     : tc_launch<0, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, stream);

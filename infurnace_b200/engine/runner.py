@@ -198,12 +198,14 @@ class ModelRunner:
             n = len(e.tokens)
             if n < 1:
                 raise BatchError(f"request {e.request_id!r} brings no tokens")
-            for t in e.tokens:
-                if not placeholders and not 0 <= int(t) < vocab:
-                    raise BatchError(f"token id {t} of request {e.request_id!r} is outside the vocabulary of {vocab}")
-            for w in e.want:
-                if not 0 <= int(w) < n:
-                    raise BatchError(f"request {e.request_id!r} wants logits at place {w} of {n} tokens")
+            if not placeholders:
+                lo, hi = (min(e.tokens), max(e.tokens)) if n > 1 else (e.tokens[0], e.tokens[0])
+                if not 0 <= int(lo) or not int(hi) < vocab:
+                    bad = next(t for t in e.tokens if not 0 <= int(t) < vocab)
+                    raise BatchError(f"token id {bad} of request {e.request_id!r} is outside the vocabulary of {vocab}")
+            if len(e.want) and not (0 <= int(min(e.want)) and int(max(e.want)) < n):
+                bad = next(w for w in e.want if not 0 <= int(w) < n)
+                raise BatchError(f"request {e.request_id!r} wants logits at place {bad} of {n} tokens")
             if self.cache.num_computed(e.request_id) + n > self.max_model_len:
                 raise BatchError(f"request {e.request_id!r} would grow past max_model_len {self.max_model_len}")
             total += n
@@ -401,37 +403,8 @@ class ModelRunner:
             self._stage_events[turn].synchronize()
         host_small, host_tables = self._stage[turn]
         np_small, np_tables = self._stage_np[turn]
-        ids, pos, req, rows, cu, seq, slots, first = [], [], [], [], [0], [], [], []
-        group_slots = [[] for _ in cache.kv_groups]
-        max_q, min_q = 0, 1 << 30
-        for r, e in enumerate(entries):
-            start = cache.num_computed(e.request_id)
-            n = len(e.tokens)
-            base = len(ids)
-            ids.extend(max(0, int(t)) for t in e.tokens)
-            pos.extend(range(start, start + n))
-            req.extend([r] * n)
-            rows.extend(base + int(w) for w in e.want)
-            cu.append(base + n)
-            seq.append(start + n)
-            slots.append(cache.slot_of(e.request_id))
-            first.append(1 if start == 0 else 0)
-            max_q, min_q = max(max_q, n), min(min_q, n)
-            for gi in range(len(cache.kv_groups)):
-                group_slots[gi].extend(cache.slots_for(e.request_id, gi, n))
-                row = self._table_row(e.request_id, gi)
-                np_tables[gi, r, : len(row)] = row
-        real_rows = len(rows)
-        for j in range(len(entries), pad_to):      # padding of a graph bucket: tokens that store and see nothing
-            ids.append(0); pos.append(0); req.append(j); rows.append(0)
-            cu.append(cu[-1] + 1); seq.append(0); slots.append(0); first.append(0)
-            for gs in group_slots:
-                gs.append(-1)
-        N, R, M = len(ids), len(cu) - 1, len(rows)
-        if N > n_max or R > r_max or M > n_max:
-            raise BatchError(f"a step of {N} rows, {R} requests and {M} wanted rows does not fit the staging "
-                             f"regions ({n_max} rows, {r_max} requests)")
-        h = host_small
+        import numpy as np
+        n_groups = len(cache.kv_groups)
         o_ids, o_pos, o_req, o_rows = 0, n_max, 2 * n_max, 3 * n_max
         o_cu = 4 * n_max
         o_seq = o_cu + r_max + 1
@@ -439,17 +412,58 @@ class ModelRunner:
         o_first = o_slot + r_max
         o_g = o_first + r_max
         h = np_small
-        h[o_ids:o_ids + N] = ids
-        h[o_pos:o_pos + N] = pos
-        h[o_req:o_req + N] = req
-        if M:
-            h[o_rows:o_rows + M] = rows
+        total = sum(len(e.tokens) for e in entries) + max(0, pad_to - len(entries))
+        wanted = sum(len(e.want) for e in entries) + max(0, pad_to - len(entries))
+        if total > n_max or max(len(entries), pad_to) > r_max or wanted > n_max:
+            raise BatchError(f"a step of {total} rows, {max(len(entries), pad_to)} requests and {wanted} wanted rows does not "
+                             f"fit the staging regions ({n_max} rows, {r_max} requests)")
+        cu, seq, slots, first = [0], [], [], []
+        max_q, min_q = 0, 1 << 30
+        base = n_rows = 0
+        for r, e in enumerate(entries):            # whole spans at a time: a prompt portion costs no Python loop over its tokens
+            start = cache.num_computed(e.request_id)
+            n = len(e.tokens)
+            if n == 1:                              # a decoded token: plain scalar writes beat array calls
+                h[o_ids + base] = max(0, int(e.tokens[0]))
+                h[o_pos + base] = start
+                h[o_req + base] = r
+                for w in e.want:
+                    h[o_rows + n_rows] = base + int(w)
+                    n_rows += 1
+            else:
+                h[o_ids + base:o_ids + base + n] = np.maximum(np.asarray(e.tokens, dtype=np.int64), 0)
+                h[o_pos + base:o_pos + base + n] = np.arange(start, start + n, dtype=np.int32)
+                h[o_req + base:o_req + base + n] = r
+                k = len(e.want)
+                if k:
+                    h[o_rows + n_rows:o_rows + n_rows + k] = np.asarray(e.want, dtype=np.int64) + base
+                    n_rows += k
+            cu.append(base + n)
+            seq.append(start + n)
+            slots.append(cache.slot_of(e.request_id))
+            first.append(1 if start == 0 else 0)
+            max_q, min_q = max(max_q, n), min(min_q, n)
+            for gi in range(n_groups):
+                if n == 1:
+                    h[o_g + gi * n_max + base] = cache.slots_for(e.request_id, gi, 1)[0]
+                else:
+                    h[o_g + gi * n_max + base:o_g + gi * n_max + base + n] = cache.slots_array(e.request_id, gi, n)
+                row = self._table_row(e.request_id, gi)
+                np_tables[gi, r, : len(row)] = row
+            base += n
+        real_rows = n_rows
+        for j in range(len(entries), pad_to):      # padding of a graph bucket: tokens that store and see nothing
+            h[o_ids + base] = 0; h[o_pos + base] = 0; h[o_req + base] = j; h[o_rows + n_rows] = 0
+            for gi in range(n_groups):
+                h[o_g + gi * n_max + base] = -1
+            cu.append(cu[-1] + 1); seq.append(0); slots.append(0); first.append(0)
+            base += 1; n_rows += 1
+        N, R, M = base, len(cu) - 1, n_rows
         h[o_cu:o_cu + R + 1] = cu
         h[o_seq:o_seq + R] = seq
         h[o_slot:o_slot + R] = slots
         h[o_first:o_first + R] = first
-        for gi, gs in enumerate(group_slots):
-            h[o_g + gi * n_max: o_g + gi * n_max + N] = gs
+        group_slots = cache.kv_groups
         o_f = o_g + len(group_slots) * n_max
         if temperatures is not None:
             hf = h.view("float32")

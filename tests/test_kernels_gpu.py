@@ -159,6 +159,40 @@ def test_qk_norm_rope_store(K, dtype, nq, nkv, d, rdim, inter, ps):
     assert torch.equal(before, qkv_gpu) and torch.equal(kv2, kv_gpu)
 
 
+@pytest.mark.parametrize("nq,nkv,ps,norm,rotate", [(16, 8, 16, True, True), (3, 3, 8, True, True), (5, 1, 32, False, True),
+                                                   (4, 2, 16, True, False)])
+def test_qk_norm_rope_store_for_many_tokens_of_head_size_128(K, nq, nkv, ps, norm, rotate):
+    """Steps of 64 tokens and more with bfloat16 heads of 128 run the form in which half a warp takes a head with 16
+    bytes per lane (any number of heads, also odd ones); against the plain statement, with the angles from the table."""
+    n, d, pages = 150, 128, 12
+    qkv = rnd((n, (nq + 2 * nkv) * d), torch.bfloat16, 6)
+    qw = (1 + 0.1 * rnd((d,), torch.float32, 7)).to(torch.bfloat16) if norm else None
+    kw = (1 + 0.1 * rnd((d,), torch.float32, 8)).to(torch.bfloat16) if norm else None
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    positions = torch.randint(0, 5000, (n,), dtype=torch.int32)
+    slots = torch.randperm(pages * ps)[:n].to(torch.int32) if pages * ps >= n else torch.arange(n, dtype=torch.int32) % (pages * ps)
+    if pages * ps < n:
+        pages = -(-n // ps)
+        slots = torch.randperm(pages * ps)[:n].to(torch.int32)
+    slots[3] = -1
+    kv_ref = torch.zeros((pages, 2, nkv, ps, d), dtype=torch.bfloat16)
+    qkv_ref = qkv.clone()
+    ReferenceKernels(torch.float32).qk_norm_rope_store(qkv_ref, nq, nkv, d, qw, kw, 1e-6, inv_freq if rotate else None,
+                                                       d if rotate else 0, False, positions, slots, kv_ref)
+    table = None
+    if rotate:
+        table = torch.empty((n, d), dtype=torch.float32, device="cuda")
+        K.rope_table(positions.cuda(), inv_freq.cuda(), table)
+    kv_gpu, qkv_gpu = torch.zeros_like(kv_ref, device="cuda"), qkv.cuda()
+    K.qk_norm_rope_store(qkv_gpu, nq, nkv, d, qw.cuda() if norm else None, kw.cuda() if norm else None, 1e-6,
+                         inv_freq.cuda() if rotate else None, d if rotate else 0, False, positions.cuda(), slots.cuda(), kv_gpu,
+                         rope_table=table)
+    t = dict(rtol=1.6e-2, atol=2e-2)
+    torch.testing.assert_close(qkv_gpu.cpu().float(), qkv_ref.float(), **t)
+    torch.testing.assert_close(kv_gpu.cpu().float(), kv_ref.float(), **t)
+    assert kv_gpu.cpu()[kv_ref == 0].abs().max() == 0
+
+
 @pytest.mark.parametrize("n", [1, 5, 8, 13, 16])
 @pytest.mark.parametrize("nq,nkv,d,k,ps", [(16, 8, 128, 1024, 16), (4, 2, 64, 2048, 8), (2, 1, 256, 4096, 32), (3, 3, 128, 136, 16)])
 @pytest.mark.parametrize("norm,rotate,scaled", [(True, True, False), (True, True, True), (False, True, False), (True, False, False)])
@@ -375,7 +409,7 @@ def test_linear_skinny(K, od, n, o, k, splits, epilogue):
 @pytest.mark.parametrize("n,o,k", [(128, 128, 64), (65, 72, 72), (300, 333, 136), (2048, 1024, 1024), (130, 200, 1000),
                                    (257, 4096, 3072), (1000, 151936 // 64, 520)])
 @pytest.mark.parametrize("epilogue", ["none", "silu_gate"])
-@pytest.mark.parametrize("shape", [0, 1, 2, 3])
+@pytest.mark.parametrize("shape", [0, 1, 2, 3, 4, 5])
 def test_linear_tcgen05(K, od, n, o, k, epilogue, shape):
     """The many-rows product on tcgen05 (TMA in, tensor memory accumulator): tiles that hang over
     the ends of all three dimensions, both epilogues, and each tile shape (0: the library's choice,
