@@ -78,7 +78,7 @@ __device__ __forceinline__ void gv_cluster_barrier() {
 // out = silu(gate) * up.  EPI 2: v = x + y is written back to x, out = v * g.  WARPS: warps of a CTA (they split k).
 // STAGES: steps of 128 of k whose weights (and, for one block of tokens, activations) a warp has requested at any
 // time.  1: every warp's k range is one step (the sizes of small models, where the chain of round trips counts);
-// 2 or 3: a warp walks a long k range and keeps the memory pipe full while it multiplies (large models, where the
+// 2: a warp walks a long k range and keeps the memory pipe full while it multiplies (large models, where the
 // bytes count).
 template <int NB, int EPI, int WARPS, typename TO, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -401,7 +401,7 @@ static int gv_by_n(int nb, const void* x, const void* w, void* out, int n, int o
   }
 }
 
-// plan 0: chosen from the sizes.  Otherwise warps * 10 + stages, one of 81, 161, 241, 82, 83 (for measurements).
+// plan 0: chosen from the sizes.  Otherwise warps * 10 + stages, one of 81, 161, 241, 82 (for measurements).
 static int g_gv_plan = 0;
 IFB_EXPORT void ifb_linear_gemv_set_plan(int plan) { g_gv_plan = plan; }
 
@@ -416,7 +416,7 @@ static int gv_by_k(int nb, const void* x, const void* w, void* out, int n, int o
     if (k <= 1024) plan = 81;
     else if (k <= 2048) plan = 161;
     else if (k <= 3072 && nb <= 2) plan = 241;
-    else plan = 82;       // two stages: three measured slower at every size (registers leave one CTA per SM)
+    else plan = 82;       // two stages: a third measured slower at every size (its registers leave one CTA per SM)
   }
   switch (plan) {
     case 81: return gv_by_n<EPI, 8, TO, 1>(nb, x, w, out, n, o, k, rs, res, s);
@@ -426,9 +426,6 @@ static int gv_by_k(int nb, const void* x, const void* w, void* out, int n, int o
       if (nb == 2) return gv_launch<2, EPI, 24, TO, 1>(x, w, out, n, o, k, rs, res, s);
       return gv_by_n<EPI, 16, TO, 1>(nb, x, w, out, n, o, k, rs, res, s);
     case 82: return gv_by_n<EPI, 8, TO, 2>(nb, x, w, out, n, o, k, rs, res, s);
-    case 83:
-      if (nb == 1) return gv_launch<1, EPI, 8, TO, 3>(x, w, out, n, o, k, rs, res, s);
-      return gv_by_n<EPI, 8, TO, 2>(nb, x, w, out, n, o, k, rs, res, s);
     default: return IFB_ERR_ARG;
   }
 }

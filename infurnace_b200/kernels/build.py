@@ -25,7 +25,8 @@ from ..errors import KernelError
 
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
-BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+              "--threads", "4"]      # the sources of a library are compiled side by side
 
 # library name -> (sources, extra flags); sources are file names under csrc, or absolute paths (register_library)
 LIBRARIES: Dict[str, tuple] = {
