@@ -6,7 +6,8 @@ cudaMalloc's device-wide synchronisation is not allowed.  For them the library c
 product's split-k scratch inside its own device image.  This test calls that entry point through
 its exported C symbol, twice in a row with different inputs (the scratch keeps what the first call
 left in it), and compares each result with the ordinary entry point's, which takes its scratch from
-the caller.  It runs last, so that a run that stops at the first failure has seen every other test.
+the caller, and with the plain statement of the product in float64, so that the test stands on its
+own.  It runs last, so that a run that stops at the first failure has seen every other test.
 """
 import ctypes
 from ctypes import c_int, c_void_p
@@ -59,6 +60,12 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(n, o, k, splits, ep
         torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2 if out_dtype == torch.bfloat16 else 2e-4,
                                    atol=2e-3 if out_dtype == torch.bfloat16 else 1e-4)
         assert torch.equal(got, want)
+        # and both are the product: against the plain statement in float64
+        from kernel_refs import ReferenceKernels
+        ref = torch.empty((n, o), dtype=torch.float64)
+        ReferenceKernels(torch.float64).linear(x.cpu(), w.cpu(), ref, "silu_gate" if epilogue else "none")
+        torch.testing.assert_close(got.cpu().double(), ref, rtol=1.6e-2 if out_dtype == torch.bfloat16 else 2e-4,
+                                   atol=2e-3 if out_dtype == torch.bfloat16 else 1e-4)
 
 
 def test_sizes_beyond_the_scratch_are_refused():
