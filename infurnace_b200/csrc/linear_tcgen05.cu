@@ -122,16 +122,81 @@ __device__ __forceinline__ float fast_rcp(float x) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
+// All threads of all CTAs of the cluster: arrive (release) and wait (acquire).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Four floats at this CTA's shared address `addr`, read from the CTA of rank `rank` in the cluster.
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr, int rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(addr), "r"(rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128 bytes, groups of 8
 // rows 1024 bytes apart (stride byte offset), leading byte offset unused (1), descriptor version 1.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// A normalisation folded into the products around it (RMSNorm(v) = v * g * r with one r per row): the product that
+// makes v (plain epilogue) adds the residual stream, writes v back to it, writes v * g as its output and leaves sums of
+// v^2 over slices of the features; the product that reads v * g multiplies its rows by r, from those sums added in a
+// fixed order, before its own epilogue.  No kernel runs for the norm itself.
+struct TcFold {
+  const float* rs_partials;   // reading side: [rs_parts][n_rows] sums of squares (null: rows are not scaled)
+  int rs_parts;
+  float rs_eps, rs_inv_width; // r = rsqrt(sum * inv_width + eps)
+  float* res_x;               // making side: [n_rows][o_out] float32 residual stream, v = x + y in place (null: plain)
+  const void* res_g;          // [o_out] norm weight
+  int res_g_dtype;
+  float* res_partials;        // [parts][n_rows], written; what a part covers depends on the launch (tc_fold_parts)
+};
+__device__ __forceinline__ float tc_row_factor(const TcFold& f, int row, int n_rows) {
+  if (!f.rs_partials || row >= n_rows) return 1.f;
+  float sum = 0.f;
+#pragma unroll 4
+  for (int p = 0; p < f.rs_parts; ++p) sum += __ldg(f.rs_partials + (size_t)p * n_rows + row);
+  return rsqrtf(sum * f.rs_inv_width + f.rs_eps);
+}
+// v = x + y for 32 consecutive features of one row (x updated in place), y <- v * g; returns the sum of v^2.
+__device__ __forceinline__ float tc_residual_chunk(const TcFold& f, float (&y)[32], int row, int n_rows, int col0, int o_out) {
+  float ss = 0.f;
+  if (row >= n_rows) return 0.f;
+  float* xr = f.res_x + (size_t)row * o_out + col0;
+  if (col0 + 32 <= o_out && (o_out & 3) == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      float4 xv = *reinterpret_cast<float4*>(xr + j);
+      xv.x += y[j]; xv.y += y[j + 1]; xv.z += y[j + 2]; xv.w += y[j + 3];
+      *reinterpret_cast<float4*>(xr + j) = xv;
+      ss += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+      y[j] = xv.x * load_as_f32(f.res_g, f.res_g_dtype, col0 + j);
+      y[j + 1] = xv.y * load_as_f32(f.res_g, f.res_g_dtype, col0 + j + 1);
+      y[j + 2] = xv.z * load_as_f32(f.res_g, f.res_g_dtype, col0 + j + 2);
+      y[j + 3] = xv.w * load_as_f32(f.res_g, f.res_g_dtype, col0 + j + 3);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < o_out) {
+        const float v = xr[j] + y[j];
+        xr[j] = v;
+        ss += v * v;
+        y[j] = v * load_as_f32(f.res_g, f.res_g_dtype, col0 + j);
+      }
+  }
+  return ss;
+}
+
 template <typename Cfg, typename TO>
 __global__ void __launch_bounds__(G_THREADS)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                      TO* __restrict__ out, int n_rows, int o_out, int k_dim, int* __restrict__ err) {
+                      TO* __restrict__ out, int n_rows, int o_out, int k_dim, int* __restrict__ err,
+                      int splits, TcFold fold) {
   constexpr int EPI = Cfg::EPI, MH = Cfg::MH, NACC = Cfg::NACC, FO = Cfg::FO;
   extern __shared__ unsigned char g_smem_raw[];
   const uint32_t raw = g_smem_u32(g_smem_raw);
@@ -143,7 +208,14 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;     // warp-uniform
   const int m0 = blockIdx.y * (MH * G_BM), n0 = blockIdx.x * FO;
-  const int kblocks = (k_dim + G_BK - 1) / G_BK;
+  // With splits > 1 (plain epilogue, one 128-row tile per CTA) the CTAs of a tile are a cluster along z: CTA z
+  // multiplies the z-th part of the k range, leaves its float32 tile in its shared memory, and after a cluster barrier
+  // adds, in the order of z, a slice of the tile's rows over all CTAs' copies and stores it.
+  const int kb_all = (k_dim + G_BK - 1) / G_BK;
+  const int kb_per = (kb_all + splits - 1) / splits;
+  const int kb0 = blockIdx.z * kb_per;
+  const int kblocks = max(0, min(kb_all, kb0 + kb_per) - kb0);    // this CTA's k blocks are kb0 .. kb0 + kblocks - 1
+  constexpr int RED_PITCH = FO + 4;                               // floats per row of the tile left in shared memory
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -167,8 +239,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       for (int kb = 0; kb < first; ++kb) {
         unsigned char* stage = smem + kb * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full[kb], Cfg::STAGE_BYTES);
-        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[kb], kb * G_BK, n0);               // FO rows of w
-        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[kb], kb * G_BK, o_out + n0);
+        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[kb], (kb0 + kb) * G_BK, n0);       // FO rows of w
+        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[kb], (kb0 + kb) * G_BK, o_out + n0);
       }
     }
     __syncwarp();
@@ -176,7 +248,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     ifb_pdl_trigger();
     if (elect_one()) {
       for (int kb = 0; kb < first; ++kb)
-        tma_load_2d(smem + kb * Cfg::STAGE_BYTES, &tmap_x, &full[kb], kb * G_BK, m0);       // MH * 128 rows of x
+        tma_load_2d(smem + kb * Cfg::STAGE_BYTES, &tmap_x, &full[kb], (kb0 + kb) * G_BK, m0);   // MH * 128 rows of x
     }
     __syncwarp();
     for (int kb = first; kb < kblocks; ++kb) {
@@ -186,9 +258,9 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       if (elect_one()) {
         unsigned char* stage = smem + s * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-        tma_load_2d(stage, &tmap_x, &full[s], kb * G_BK, m0);
-        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[s], kb * G_BK, n0);
-        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[s], kb * G_BK, o_out + n0);
+        tma_load_2d(stage, &tmap_x, &full[s], (kb0 + kb) * G_BK, m0);
+        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[s], (kb0 + kb) * G_BK, n0);
+        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[s], (kb0 + kb) * G_BK, o_out + n0);
       }
       __syncwarp();
     }
@@ -229,14 +301,17 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     static_assert(8 * 32 * PITCH <= Cfg::STAGES * Cfg::STAGE_BYTES, "the staging rows must fit in the stages");
     const int q = warp & 3;                                      // this warp's quarter of the 128 lanes
     const int c_lo = ((warp - 2) >> 2) * CW;                     // and its half of the tile's features
-    if (mbar_wait(accum, 0, abort_flag, err, 3)) {
+    if (kblocks > 0 && mbar_wait(accum, 0, abort_flag, err, 3)) {
       tc_fence_after();
+      if (fold.rs_partials || fold.res_x) ifb_pdl_wait();         // what the predecessor wrote is read here directly
       const bool vec = ((size_t)o_out * sizeof(TO)) % 16 == 0 && (((uintptr_t)out) & 15) == 0 && n0 + c_lo + CW <= o_out;
       unsigned char* buf = smem + (warp - 2) * (32 * PITCH);
 #pragma unroll 1
       for (int hf = 0; hf < MH; ++hf) {
         const int row0 = m0 + hf * G_BM + q * 32;
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + hf * NACC;
+        const float rfac = tc_row_factor(fold, row0 + lane, n_rows);
+        float ss = 0.f;                                          // this row's v^2 over this warp's features
 #pragma unroll 1
        for (int p0 = c_lo; p0 < c_lo + CW; p0 += PW) {
 #pragma unroll 1
@@ -253,13 +328,20 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
             for (int j = 0; j < 32; ++j) {
               // silu(g) * u with the hardware's exp2 and reciprocal (relative error about 1e-6; the result is
               // rounded to the output type)
-              const float g = __uint_as_float(v[j]);
-              y[j] = g * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * g)) * __uint_as_float(u[j]);
+              const float g = __uint_as_float(v[j]) * rfac;
+              y[j] = g * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * g)) * (__uint_as_float(u[j]) * rfac);
             }
           } else {
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
+            for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]) * rfac;
+          }
+          if (!EPI && splits == 1 && fold.res_x) ss += tc_residual_chunk(fold, y, row0 + lane, n_rows, n0 + c0, o_out);
+          if (splits > 1) {                                      // the part stays here for the cluster's sum
+            float* dst = reinterpret_cast<float*>(smem) + (size_t)(hf * G_BM + q * 32 + lane) * RED_PITCH + c0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+            continue;
           }
           if (vec) {
             unsigned char* dst = buf + lane * PITCH + (c0 - p0) * (int)sizeof(TO);
@@ -285,7 +367,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
               if (n0 + c0 + j < o_out) dst[j] = from_f32<TO>(y[j]);
           }
         }
-        if (vec) {
+        if (vec && splits == 1) {
           __syncwarp();
           unsigned char* obase = reinterpret_cast<unsigned char*>(out + (size_t)row0 * o_out + n0 + p0);
 #pragma unroll 4
@@ -297,8 +379,60 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           __syncwarp();                                          // before the next rows overwrite the buffer
         }
        }
+       if (!EPI && splits == 1 && fold.res_x && row0 + lane < n_rows)
+         fold.res_partials[(size_t)(blockIdx.x * 2 + (c_lo ? 1 : 0)) * n_rows + row0 + lane] = ss;
       }
     }
+  }
+  if (splits > 1) {
+    cluster_sync_all();                        // every CTA's part is in its shared memory
+    if (fold.res_x) ifb_pdl_wait();
+    const int rows = min(G_BM, n_rows - m0), cols = min(FO, o_out - n0);
+    const int used = (kb_all + kb_per - 1) / kb_per;                       // CTAs that had k blocks
+    const int per = (rows + splits - 1) / splits;
+    const int r_lo = blockIdx.z * per, r_hi = min(rows, r_lo + per);
+    const bool vec = ((size_t)o_out * sizeof(TO)) % 16 == 0 && (((uintptr_t)out) & 15) == 0 && cols == FO;
+    const uint32_t tile_addr = g_smem_u32(smem);
+    for (int i = threadIdx.x; i < (r_hi - r_lo) * (FO / 4); i += G_THREADS) {
+      const int r = r_lo + i / (FO / 4), c = (i % (FO / 4)) * 4;
+      const uint32_t at = tile_addr + (uint32_t)((r * RED_PITCH + c) * 4);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int z = 0; z < used; ++z) {
+        const float4 v = ld_cluster_f4(at, z);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      TO* dst = out + (size_t)(m0 + r) * o_out + n0 + c;
+      if (fold.res_x) {
+        // a warp holds one row of the tile: v = x + y, x <- v, the output becomes v * g, the warp's sum of v^2 one part
+        float* xr = fold.res_x + (size_t)(m0 + r) * o_out + n0 + c;
+        float yv[4] = {acc.x, acc.y, acc.z, acc.w}, ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (c + j < cols) {
+            const float v = xr[j] + yv[j];
+            xr[j] = v;
+            ss += v * v;
+            yv[j] = v * load_as_f32(fold.res_g, fold.res_g_dtype, n0 + c + j);
+          }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+        if ((threadIdx.x & 31) == 0) fold.res_partials[(size_t)blockIdx.x * n_rows + m0 + r] = ss;
+        acc = make_float4(yv[0], yv[1], yv[2], yv[3]);
+      }
+      if (vec) {
+        if (sizeof(TO) == 4) {
+          *reinterpret_cast<float4*>(dst) = acc;
+        } else {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+          *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
+      } else {
+        const float y[4] = {acc.x, acc.y, acc.z, acc.w};
+        for (int j = 0; j < 4; ++j)
+          if (c + j < cols) dst[j] = from_f32<TO>(y[j]);
+      }
+    }
+    cluster_sync_all();                        // nobody leaves while its shared memory is being read
   }
   if (*abort_flag) {                         // a wait gave up: let copies in flight land before the CTA goes away
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -343,7 +477,7 @@ template <typename Cfg, typename TO>
 __global__ void __launch_bounds__(G_THREADS, 1)
 linear_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                                  TO* __restrict__ out, int n_rows, int o_out, int k_dim, int tiles_m, int tiles_total,
-                                 int* __restrict__ err) {
+                                 int* __restrict__ err, TcFold fold) {
   constexpr int EPI = Cfg::EPI, NACC = Cfg::NACC, FO = Cfg::FO, STAGES = Cfg::STAGES;
   extern __shared__ unsigned char g_smem_raw[];
   const uint32_t raw = g_smem_u32(g_smem_raw);
@@ -460,6 +594,8 @@ linear_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, con
       const bool vec = ((size_t)o_out * sizeof(TO)) % 16 == 0 && (((uintptr_t)out) & 15) == 0 && n0 + c_lo + CW <= o_out;
       const int row0 = m0 + q * 32;
       const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + b * NACC;
+      if (fold.rs_partials && it == 0) ifb_pdl_wait();             // the sums are the predecessor's: read them after it
+      const float rfac = tc_row_factor(fold, row0 + lane, n_rows);
 #pragma unroll 1
       for (int p0 = c_lo; p0 < c_lo + CW; p0 += PW) {
         if (n0 + p0 >= o_out) break;                             // warp-uniform
@@ -474,13 +610,13 @@ linear_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, con
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float gte = __uint_as_float(v[j]);
-              y[j] = gte * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * gte)) * __uint_as_float(u[j]);
+              const float gte = __uint_as_float(v[j]) * rfac;
+              y[j] = gte * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * gte)) * (__uint_as_float(u[j]) * rfac);
             }
           } else {
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
+            for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]) * rfac;
           }
           if (vec) {
             unsigned char* dst = buf + lane * PITCH + (c0 - p0) * (int)sizeof(TO);
@@ -533,7 +669,8 @@ linear_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, con
 }
 
 template <typename Cfg, typename TO>
-static int tc_launch_persistent(const void* x, const void* w, void* out, int n, int o, int k, int* err, int sm_count, cudaStream_t s) {
+static int tc_launch_persistent(const void* x, const void* w, void* out, int n, int o, int k, int* err, int sm_count, cudaStream_t s,
+                                const TcFold& fold) {
   CUtensorMap mx, mw;
   int st = make_map(&mx, x, n, k, G_BM);
   if (st) return st;
@@ -545,76 +682,163 @@ static int tc_launch_persistent(const void* x, const void* w, void* out, int n, 
   const int total = (int)(tiles_m * tiles_n);
   const int grid = total < sm_count ? total : sm_count;
   return ifb_launch(linear_tcgen05_persistent_kernel<Cfg, TO>, dim3(grid), dim3(G_THREADS), (size_t)Cfg::SMEM_BYTES, s, mx, mw, (TO*)out, n,
-                    o, k, (int)tiles_m, total, err);
+                    o, k, (int)tiles_m, total, err, fold);
 }
 
 template <typename Cfg, typename TO>
-static int tc_launch_cfg(const void* x, const void* w, void* out, int n, int o, int k, int* err, cudaStream_t s) {
+static int tc_launch_cfg(const void* x, const void* w, void* out, int n, int o, int k, int* err, cudaStream_t s, const TcFold& fold,
+                         int splits = 1) {
   CUtensorMap mx, mw;
   int st = make_map(&mx, x, n, k, Cfg::MH * G_BM);
   if (st) return st;
   st = make_map(&mw, w, Cfg::EPI ? 2 * o : o, k, Cfg::EPI ? Cfg::NACC / 2 : Cfg::NACC);
   if (st) return st;
   IFB_ALLOW_SMEM((linear_tcgen05_kernel<Cfg, TO>), Cfg::SMEM_BYTES);
-  dim3 grid((o + Cfg::FO - 1) / Cfg::FO, (n + Cfg::MH * G_BM - 1) / (Cfg::MH * G_BM));
+  dim3 grid((o + Cfg::FO - 1) / Cfg::FO, (n + Cfg::MH * G_BM - 1) / (Cfg::MH * G_BM), splits);
   if (grid.y > 65535) return IFB_ERR_SIZE;
-  return ifb_launch(linear_tcgen05_kernel<Cfg, TO>, grid, dim3(G_THREADS), (size_t)Cfg::SMEM_BYTES, s, mx, mw, (TO*)out, n, o, k, err);
+  if (splits == 1)
+    return ifb_launch(linear_tcgen05_kernel<Cfg, TO>, grid, dim3(G_THREADS), (size_t)Cfg::SMEM_BYTES, s, mx, mw, (TO*)out, n, o, k, err, 1, fold);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(G_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ifb_pdl_enabled() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_tcgen05_kernel<Cfg, TO>, mx, mw, (TO*)out, n, o, k, err, splits, fold);
+  if (e != cudaSuccess) { cudaGetLastError(); return -(int)e; }
+  return IFB_OK;
 }
 
 // The shape of the tiles: a wave of wide tiles does four 128 x 128 products per SM in little more time than a wave of
 // narrow tiles (two CTAs per SM) does two, but only if there are enough wide tiles to fill the SMs.  shape: 0 chooses
 // (see below), 1 narrow, 2 deep, 3 wide, 4 and 5 persistent (for tests and measurements).
-template <int EPI, typename TO>
-static int tc_launch(const void* x, const void* w, void* out, int n, int o, int k, int* err, int shape, cudaStream_t s) {
+static int tc_sm_count() {
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       sm_count = 1;
   }
+  return sm_count;
+}
+// By measurement.  With the silu_gate epilogue: the persistent kernel (its tile already accumulates 256 columns per
+// product, and the heavy epilogue of one tile runs beside the products of the next).  Otherwise one tile per CTA:
+// the wide shape when there are enough wide tiles to fill the SMs (a 256 x 256 tile reads half the operand bytes
+// per product from shared memory, which is what bounds these kernels), else the deep or the narrow one.
+static int tc_pick_shape(int epi, int n, int o) {
+  if (epi) return 4;
+  const int sm_count = tc_sm_count();
+  const long long tn = (long long)((o + 127) / 128) * ((n + G_BM - 1) / G_BM);
+  const long long tw = (long long)((o + 255) / 256) * ((n + 2 * G_BM - 1) / (2 * G_BM));
+  const double cost_narrow = (double)((tn + 2 * sm_count - 1) / (2 * sm_count));
+  const double cost_wide = (double)((tw + sm_count - 1) / sm_count) * 1.15;
+  return (n > G_BM && cost_wide < cost_narrow) ? 3 : (tn <= sm_count ? 2 : 1);
+}
+
+template <int EPI, typename TO>
+static int tc_launch(const void* x, const void* w, void* out, int n, int o, int k, int* err, int shape, int splits, const TcFold& fold,
+                     cudaStream_t s) {
   using Narrow = GemmCfg<EPI, 1, EPI ? 256 : 128, EPI ? 2 : 3>;
   using Deep = GemmCfg<EPI, 1, EPI ? 256 : 128, EPI ? 4 : 6>;
   using Wide = GemmCfg<EPI, 2, 256, 3>;
   using P128 = PersistCfg<EPI, EPI ? 256 : 128, EPI ? 3 : 5>;      // 128 features per tile
   using P256 = PersistCfg<EPI, 256, 3>;                            // 256 features per tile (plain epilogue only)
-  if (shape == 0) {
-    // By measurement.  With the silu_gate epilogue: the persistent kernel (its tile already accumulates 256 columns per
-    // product, and the heavy epilogue of one tile runs beside the products of the next).  Otherwise one tile per CTA:
-    // the wide shape when there are enough wide tiles to fill the SMs (a 256 x 256 tile reads half the operand bytes
-    // per product from shared memory, which is what bounds these kernels), else the deep or the narrow one.
-    if (EPI) {
-      shape = 4;
-    } else {
-      const long long tn = (long long)((o + Narrow::FO - 1) / Narrow::FO) * ((n + G_BM - 1) / G_BM);
-      const long long tw = (long long)((o + Wide::FO - 1) / Wide::FO) * ((n + 2 * G_BM - 1) / (2 * G_BM));
-      const double cost_narrow = (double)((tn + 2 * sm_count - 1) / (2 * sm_count));
-      const double cost_wide = (double)((tw + sm_count - 1) / sm_count) * 1.15;
-      shape = (n > G_BM && cost_wide < cost_narrow) ? 3 : (tn <= sm_count ? 2 : 1);
-    }
+  if (splits > 1) {
+    static_assert(G_BM * (Deep::FO + 4) * 4 <= Narrow::STAGES * Narrow::STAGE_BYTES, "the float32 tile must fit in the stages");
+    if (EPI || splits > 8) return IFB_ERR_ARG;
+    // one tile of rows: a CTA per SM with a deep ring; more: two CTAs per SM, one's sum beside the other's products
+    if (n <= G_BM && shape != 1) return tc_launch_cfg<Deep, TO>(x, w, out, n, o, k, err, s, fold, splits);
+    return tc_launch_cfg<Narrow, TO>(x, w, out, n, o, k, err, s, fold, splits);
   }
-  if (shape == 5 && !EPI) return tc_launch_persistent<P256, TO>(x, w, out, n, o, k, err, sm_count, s);
-  if (shape == 4 || shape == 5) return tc_launch_persistent<P128, TO>(x, w, out, n, o, k, err, sm_count, s);
-  if (shape == 3) return tc_launch_cfg<Wide, TO>(x, w, out, n, o, k, err, s);
-  if (shape == 2) return tc_launch_cfg<Deep, TO>(x, w, out, n, o, k, err, s);
-  return tc_launch_cfg<Narrow, TO>(x, w, out, n, o, k, err, s);
+  if (shape == 0) shape = tc_pick_shape(EPI, n, o);
+  if (fold.res_x && (EPI || shape > 3)) return IFB_ERR_ARG;        // the making side is the one-tile kernel's
+  if (shape == 5 && !EPI) return tc_launch_persistent<P256, TO>(x, w, out, n, o, k, err, tc_sm_count(), s, fold);
+  if (shape == 4 || shape == 5) return tc_launch_persistent<P128, TO>(x, w, out, n, o, k, err, tc_sm_count(), s, fold);
+  if (shape == 3) return tc_launch_cfg<Wide, TO>(x, w, out, n, o, k, err, s, fold);
+  if (shape == 2) return tc_launch_cfg<Deep, TO>(x, w, out, n, o, k, err, s, fold);
+  return tc_launch_cfg<Narrow, TO>(x, w, out, n, o, k, err, s, fold);
 }
 
 // x [n_rows, k] and w [out_features (x2 for the silu_gate epilogue), k] bfloat16, 16-byte aligned, k a multiple of 8;
 // out bfloat16 or float32.  `err` points to a device int that stays 0 unless a bounded wait gave up.  shape: 0 lets the
-// library choose (the persistent kernel), 1-3 force the one-tile-per-CTA kernel narrow, deep or wide, 4 and 5 the
-// persistent kernel with tiles of 128 or 256 features.
-IFB_EXPORT int ifb_linear_tcgen05(const void* x, const void* w, void* out, int out_dtype, int n_rows, int out_features,
-                                  int k_dim, int epilogue, int* err, int shape, cudaStream_t stream) {
+// library choose, 1-3 force the one-tile-per-CTA kernel narrow, deep or wide, 4 and 5 the persistent kernel with tiles
+// of 128 or 256 features.  splits 2 to 8 (plain epilogue): the k range of a tile of 128 x 128 is shared by a cluster of
+// that many CTAs, whose parts are added in a fixed order; for few tiles of a long k (a step of some tens of tokens).
+// scale_partials (may be null): [scale_parts][n_rows] sums of squares; output row n is multiplied by
+// rsqrt(sum_p partials[p][n] / scale_width + scale_eps) before the epilogue.
+// res_x (may be null; plain epilogue, shape 0-3): the residual stream [n_rows][out_features] float32: v = x + y is
+// written back to it, out = v * res_g, and res_partials [ifb_linear_tcgen05_fold_parts(...)][n_rows] gets sums of v^2.
+IFB_EXPORT int ifb_linear_tcgen05_ex(const void* x, const void* w, void* out, int out_dtype, int n_rows, int out_features,
+                                     int k_dim, int epilogue, int shape, int splits, const float* scale_partials, int scale_parts,
+                                     float scale_eps, int scale_width, float* res_x, const void* res_g, int res_g_dtype,
+                                     float* res_partials, int* err, cudaStream_t stream) {
   if (n_rows <= 0 || out_features <= 0) return IFB_OK;
   if (k_dim < 8 || k_dim % 8) return IFB_ERR_SIZE;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return IFB_ERR_ALIGN;
   if (epilogue != 0 && epilogue != 1) return IFB_ERR_ARG;
-  if (shape < 0 || shape > 5) return IFB_ERR_ARG;
+  if (shape < 0 || shape > 5 || splits < 0 || splits > 8) return IFB_ERR_ARG;
+  if (scale_partials && (scale_parts < 1 || scale_width < 1)) return IFB_ERR_ARG;
+  if (res_x && (!res_g || !res_partials || ((uintptr_t)res_x & 15))) return IFB_ERR_ARG;
+  const TcFold fold{scale_partials, scale_parts, scale_eps, scale_partials ? 1.f / (float)scale_width : 0.f,
+                    res_x, res_g, res_g_dtype, res_partials};
   if (out_dtype == IFB_BF16)
-    return epilogue ? tc_launch<1, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, stream)
-                    : tc_launch<0, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, stream);
+    return epilogue ? tc_launch<1, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream)
+                    : tc_launch<0, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream);
   if (out_dtype == IFB_F32)
-    return epilogue ? tc_launch<1, float>(x, w, out, n_rows, out_features, k_dim, err, shape, stream)
-                    : tc_launch<0, float>(x, w, out, n_rows, out_features, k_dim, err, shape, stream);
+    return epilogue ? tc_launch<1, float>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream)
+                    : tc_launch<0, float>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream);
   return IFB_ERR_DTYPE;
+}
+
+IFB_EXPORT int ifb_linear_tcgen05(const void* x, const void* w, void* out, int out_dtype, int n_rows, int out_features,
+                                  int k_dim, int epilogue, int* err, int shape, cudaStream_t stream) {
+  return ifb_linear_tcgen05_ex(x, w, out, out_dtype, n_rows, out_features, k_dim, epilogue, shape, 1, nullptr, 0, 0.f, 0, nullptr,
+                               nullptr, 0, nullptr, err, stream);
+}
+
+// Parts of sums of squares that a product with res_x writes per row (the launch with shape 0 and these splits).
+IFB_EXPORT int ifb_linear_tcgen05_fold_parts(int n_rows, int out_features, int splits) {
+  if (splits > 1) return (out_features + 127) / 128;
+  return tc_pick_shape(0, n_rows, out_features) == 3 ? 2 * ((out_features + 255) / 256) : 2 * ((out_features + 127) / 128);
+}
+
+using SplitCfg = GemmCfg<0, 1, 128, 6>;
+
+// How many clusters of `splits` CTAs of that kernel the device holds at a time (0 if it cannot say): a product whose
+// tiles are no more than this runs in one wave.
+IFB_EXPORT int ifb_linear_tcgen05_split_clusters(int splits) {
+  static int cached[9] = {0};
+  static bool known[9] = {false};
+  if (splits < 2 || splits > 8) return 0;
+  if (!known[splits]) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, splits);
+    cfg.blockDim = dim3(G_THREADS);
+    cfg.dynamicSmemBytes = SplitCfg::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaFuncSetAttribute(linear_tcgen05_kernel<SplitCfg, float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)SplitCfg::SMEM_BYTES) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&clusters, linear_tcgen05_kernel<SplitCfg, float>, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      clusters = 0;
+    }
+    cached[splits] = clusters;
+    known[splits] = true;
+  }
+  return cached[splits];
 }

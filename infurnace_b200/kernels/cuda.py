@@ -106,8 +106,14 @@ class CudaKernels:
         self.tc_attention_calls = 0    # launches of the tcgen05 attention kernel, of the small-q kernel, and of the latter
         self.small_q_calls = 0         # with keys and values by TMA (what ran is what tests of the product path ask)
         self.small_q_tma_calls = 0
+        self.tc_shared_k_calls = 0     # tcgen05 products with the k range shared by a cluster; with a folded norm
+        self.tc_folded_calls = 0
         self._err_armed = False
         self.tc_min_rows = 65
+        self.tc_split_min_k = int(os.environ.get("INFURNACE_TC_SPLIT_MIN_K", "512"))
+        self.tc_split_min_rows = int(os.environ.get("INFURNACE_TC_SPLIT_MIN_ROWS", "0"))     # 0: by the matrix
+        self.tc_fold_max_rows = int(os.environ.get("INFURNACE_TC_FOLD_MAX_ROWS", "128"))
+        self._tc_clusters = {}         # CTAs per cluster -> clusters of the split product that run at a time
         self._attn_mma = {}        # head size -> library
         self._attn_scratch = None
         self._attn_counters = None
@@ -180,40 +186,96 @@ class CudaKernels:
         if w.shape[1] != k or out.shape[0] != n or w.shape[0] != (2 * o if epi else o):
             raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not match")
         if row_scale is not None:
-            if not self.can_fold_norm(n, x.dtype, w) or out.dtype not in (torch.bfloat16, torch.float32):
-                raise KernelError("linear: a row scale is taken only by the few-rows bfloat16 kernel (see can_fold_norm)")
-            return self._linear_gemv(x, w, out, n, o, k, epi, row_scale)
+            if not self.can_fold_norm(n, x.dtype, w, epilogue) or out.dtype not in (torch.bfloat16, torch.float32):
+                raise KernelError("linear: a row scale is taken only by the bfloat16 kernels (see can_fold_norm)")
+            partials, parts = row_scale[0], row_scale[1]
+            _dense(partials, "row_scale partials", torch.float32)
+            if partials.dim() != 2 or partials.shape[0] < parts or partials.shape[1] != n:
+                raise KernelError("linear: row_scale partials must be [parts, rows]")
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 \
                 and out.dtype in (torch.bfloat16, torch.float32):
-            if self._on_tcgen05(n, w):
-                return self._linear_tcgen05(x, w, out, n, o, k, epi)
-            return self._linear_gemv(x, w, out, n, o, k, epi)
+            if self._on_tcgen05(n, w, epilogue):
+                splits = self.tcgen05_splits(n, o, k) if not epi else 1
+                return self._linear_tcgen05(x, w, out, n, o, k, epi, splits=splits, row_scale=row_scale)
+            return self._linear_gemv(x, w, out, n, o, k, epi, row_scale)
         self.launches += 1
         _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
                                          n, o, k, epi, self._stream()), "linear")
 
-    def _on_tcgen05(self, n, w):
+    def _on_tcgen05(self, n, w, epilogue="none", shared_k=True):
         """Which kernel a bfloat16 product of n rows against w runs on.  More than 64 rows: the tcgen05 kernel.
-        Up to 8 rows: the few-rows kernel.  Between, by measurement: the few-rows kernel re-reads the rows
-        from L2 in every CTA, so for a large weight matrix (from 2^24 elements, or from 33 rows and 4,096
-        features) the tcgen05 kernel, which streams the weights once through its tiles, is the faster one
-        although most of its 128-row tile is empty."""
+        From ``tc_split_min_rows`` rows, a product with the plain epilogue whose few tiles can share their k
+        range in clusters (:meth:`tcgen05_splits`): the tcgen05 kernel in that form, which streams a long k
+        faster than the few-rows kernel.  Else up to 8 rows: the few-rows kernel.  Between, by measurement:
+        the few-rows kernel re-reads the rows from L2 in every CTA, so for a large weight matrix (from 2^24
+        elements, or from 33 rows and 4,096 features) the tcgen05 kernel, which streams the weights once
+        through its tiles, is the faster one although most of its 128-row tile is empty."""
         if n >= self.tc_min_rows:
+            return True
+        if shared_k and epilogue == "none" and n >= self._shared_k_min_rows(w) and w.dtype == torch.bfloat16 \
+                and w.shape[1] % 8 == 0 and self.tcgen05_splits(n, w.shape[0], w.shape[1]) > 1:
             return True
         if n <= 8:
             return False
         return w.numel() >= (1 << 24) or (n >= 33 and w.shape[0] >= 4096)
 
-    def _linear_tcgen05(self, x, w, out, n, o, k, epi, shape=0):
-        """shape: 0 lets the library choose its tile shape; 1 narrow, 2 deep, 3 wide."""
+    def _shared_k_min_rows(self, w):
+        """From how many rows the tcgen05 kernel with a shared k range beats the few-rows kernel, by
+        measurement in a step's graph (o and down products of the 0.6B, 8B and 32B sizes): 17 for a small
+        matrix (the few-rows kernel is bound by its round trips, not by its bytes); 9 for a large one (a
+        second block of 8 rows costs the few-rows kernel a third more); 2 where the few-rows kernel with
+        its one CTA of 16 features per SM (long k) leaves most of its last wave empty (5,120 features:
+        320 CTAs on 148 SMs)."""
+        if self.tc_split_min_rows:
+            return self.tc_split_min_rows
+        o, k = w.shape
+        waves = -(-o // 16) / self.sm_count
+        if k > 3072 and -(-waves // 1) / waves > 1.25:
+            return 2
+        return 9 if w.numel() >= (1 << 23) else 17
+
+    def _linear_tcgen05(self, x, w, out, n, o, k, epi, shape=0, splits=1, row_scale=None, residual=None):
+        """shape: 0 lets the library choose its tile shape; 1 narrow, 2 deep, 3 wide, 4 and 5 persistent.
+        splits > 1: the k range of a tile is shared by a cluster of that many CTAs.  row_scale: as in
+        :meth:`linear`.  residual (x, norm_weight, partials): as in :meth:`linear_residual_norm`."""
+        partials, parts, eps, width = row_scale if row_scale is not None else (None, 0, 0.0, 0)
+        res_x, res_g, res_partials = residual if residual is not None else (None, None, None)
+        self.launches += 1
+        self.tc_shared_k_calls += splits > 1
+        self.tc_folded_calls += partials is not None or res_x is not None
+        self._err_armed = True
+        _check(self._tc_lib().ifb_linear_tcgen05_ex(
+            x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), n, o, k, epi, int(shape), int(splits),
+            _ptr(partials), int(parts), float(eps), int(width), _ptr(res_x), _ptr(res_g),
+            _code(res_g) if res_g is not None else 0, _ptr(res_partials), self._dev_err.data_ptr(), self._stream()), "linear")
+
+    def _tc_lib(self):
         if self._tc is None:
             self._tc = load_library("linear_tcgen05", progress=self._progress)
-            self._tc.ifb_linear_tcgen05.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                    c_void_p, c_int, c_void_p]
-        self.launches += 1
-        self._err_armed = True
-        _check(self._tc.ifb_linear_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), n, o, k, epi,
-                                           self._dev_err.data_ptr(), int(shape), self._stream()), "linear")
+            self._tc.ifb_linear_tcgen05_ex.argtypes = [
+                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float,
+                c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+            self._tc.ifb_linear_tcgen05_split_clusters.argtypes = [c_int]
+            self._tc.ifb_linear_tcgen05_fold_parts.argtypes = [c_int, c_int, c_int]
+        return self._tc
+
+    def tcgen05_splits(self, n, o, k):
+        """How many CTAs (a cluster) share the k range of a tile in the tcgen05 product of up to 512 rows:
+        the most, up to 8, whose clusters for all tiles of 128 x 128 run at the same time, each CTA
+        with at least ``tc_split_min_k`` of k; 1 if that is none."""
+        if n > 512:
+            return 1
+        tiles = -(-o // 128) * -(-n // 128)
+        for splits in range(min(8, k // self.tc_split_min_k), 1, -1):
+            if splits not in self._tc_clusters:
+                self._tc_clusters[splits] = int(self._tc_lib().ifb_linear_tcgen05_split_clusters(splits))
+            if tiles <= self._tc_clusters[splits]:
+                return splits
+        return 1
+
+    def _linear_tcgen05_split(self, x, w, out, n, o, k, splits):
+        """The one-tile kernel with the k range of a tile shared by a cluster of ``splits`` CTAs."""
+        self._linear_tcgen05(x, w, out, n, o, k, 0, splits=splits)
 
     def check_device_errors(self):
         """Raise if a kernel recorded a fault that it contained: a bounded wait on a barrier that gave
@@ -240,30 +302,43 @@ class CudaKernels:
 
     # A norm folded into the products around it: RMSNorm(v) = v * g * r with one r per row, so the product that
     # makes v writes v * g and partial sums of v^2, and the product that reads it multiplies by r at its end.
-    def can_fold_norm(self, n, dtype, w):
-        """Whether a product of ``n`` rows of ``dtype`` against ``w`` runs on the kernel that can
-        take or make a folded norm."""
-        return (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
-                and 0 < n <= min(self.gemv_max_rows, self.fold_max_rows) and not self._on_tcgen05(n, w))
+    def can_fold_norm(self, n, dtype, w, epilogue="none"):
+        """Whether a product of ``n`` rows of ``dtype`` against ``w`` (with that epilogue) takes or makes a
+        folded norm: on the tcgen05 kernel up to ``tc_fold_max_rows`` rows (one tile of rows: with many
+        rows the longer epilogue costs what the norm's own launch did), on the few-rows kernel up to
+        ``fold_max_rows``."""
+        if not (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and n > 0
+                and self.fold_max_rows > 0):
+            return False
+        if self._on_tcgen05(n, w, epilogue):
+            return n <= self.tc_fold_max_rows
+        return n <= min(self.gemv_max_rows, self.fold_max_rows)
 
-    def fold_parts(self, out_features):
-        """Partial sums per row that :meth:`linear_residual_norm` writes."""
+    def fold_parts(self, out_features, n=None, w=None):
+        """Partial sums per row that :meth:`linear_residual_norm` writes for a product of ``n`` rows against
+        ``w`` (without them: on the few-rows kernel)."""
+        if n is not None and w is not None and self._on_tcgen05(n, w):
+            splits = self.tcgen05_splits(n, w.shape[0], w.shape[1])
+            return int(self._tc_lib().ifb_linear_tcgen05_fold_parts(int(n), int(out_features), int(splits)))
         return int(self.core.ifb_linear_gemv_parts(int(out_features)))
 
     def linear_residual_norm(self, a, w, x, norm_weight, out, partials):
         """x += a w^T (x float32, in place); out = x * norm_weight (bfloat16); partials[p, n] = the sum
         of squares of row n of x over part p's features.  With ``linear(..., row_scale=(partials,
-        fold_parts(o), eps, o))`` after it this is x += a w^T followed by an RMSNorm of x."""
+        fold_parts(o, n, w), eps, o))`` after it this is x += a w^T followed by an RMSNorm of x."""
         _dense(a, "a", torch.bfloat16), _dense(w, "w", torch.bfloat16), _dense(x, "x", torch.float32)
         _dense(out, "out", torch.bfloat16), _dense(partials, "partials", torch.float32), _dense(norm_weight, "norm_weight")
         n, k = a.shape
         o = w.shape[0]
-        parts = self.fold_parts(o)
+        parts = self.fold_parts(o, n, w)
         if w.shape[1] != k or x.shape != (n, o) or out.shape != (n, o) or norm_weight.numel() != o \
                 or partials.dim() != 2 or partials.shape[0] < parts or partials.shape[1] != n:
             raise KernelError("linear_residual_norm: sizes of a, w, x, norm_weight, out and partials do not match")
         if not self.can_fold_norm(n, a.dtype, w):
-            raise KernelError("linear_residual_norm: only for few rows of bfloat16 (see can_fold_norm)")
+            raise KernelError("linear_residual_norm: only for bfloat16 (see can_fold_norm)")
+        if self._on_tcgen05(n, w):
+            return self._linear_tcgen05(a, w, out, n, o, k, 0, splits=self.tcgen05_splits(n, o, k),
+                                        residual=(x, norm_weight, partials))
         self.launches += 1
         _check(self.core.ifb_linear_gemv_residual_norm(
             a.data_ptr(), w.data_ptr(), x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight), out.data_ptr(),
@@ -301,7 +376,7 @@ class CudaKernels:
         """Whether :meth:`linear_qkv_rope_store` takes a step of ``n`` rows: few rows of bfloat16 on the few-rows
         kernel, heads of 64, 128 or 256 rotated whole in the half-split pairing (or not rotated)."""
         return (self.fused_qkv and 0 < n <= 16 and dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
-                and w_qkv.shape[1] % 8 == 0 and head_dim in (64, 128, 256) and not self._on_tcgen05(n, w_qkv)
+                and w_qkv.shape[1] % 8 == 0 and head_dim in (64, 128, 256) and not self._on_tcgen05(n, w_qkv, shared_k=False)
                 and (rotary_dim == 0 or (rotary_dim == head_dim and not interleaved))
                 and (kv_pages is None or kv_pages.dtype == torch.bfloat16))
 

@@ -28,7 +28,7 @@ class GatedMLP:
 
     def can_take_folded(self, n):
         can = getattr(self.k, "can_fold_norm", None)
-        return bool(can and can(n, self.rt.act_dtype, self.w_gate_up))
+        return bool(can and can(n, self.rt.act_dtype, self.w_gate_up, "silu_gate"))
 
     def forward(self, h, ctx, fold=None):
         h, row_scale = unfolded(h)

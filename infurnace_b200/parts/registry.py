@@ -83,7 +83,7 @@ def fold_residual_norm(kernels, ctx, tag, a, w, fold, act_dtype):
     n, o = a.shape[0], w.shape[0]
     if a.dtype != act_dtype or x.shape != (n, o) or not kernels.can_fold_norm(n, a.dtype, w):
         return None
-    parts = kernels.fold_parts(o)
+    parts = kernels.fold_parts(o, n, w)
     out = ctx.buffer("folded_" + tag, (n, o), act_dtype)
     # one flat buffer whatever the number of rows, so that its address stays the same from step to step
     partials = ctx.buffer("folded_partials_" + tag, (parts * n,), __import__("torch").float32).view(parts, n)

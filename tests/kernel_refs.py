@@ -72,10 +72,10 @@ class ReferenceKernels:
             y = g * torch.sigmoid(g) * u
         out.copy_(y.to(out.dtype))
 
-    def can_fold_norm(self, n, dtype, w):
+    def can_fold_norm(self, n, dtype, w, epilogue="none"):
         return bool(self.fold) and 0 < n <= 64
 
-    def fold_parts(self, out_features):
+    def fold_parts(self, out_features, n=None, w=None):
         return -(-out_features // 16)
 
     def linear_residual_norm(self, a, w, x, norm_weight, out, partials):

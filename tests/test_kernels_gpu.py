@@ -425,16 +425,30 @@ def test_linear_tcgen05(K, od, n, o, k, epilogue, shape):
                                atol=2e-3 if od == torch.bfloat16 else 1e-4)
 
 
-@pytest.mark.parametrize("n", [1, 8, 9, 33, 64])
-@pytest.mark.parametrize("hidden,inner,width2", [(72, 136, 40), (1000, 2048, 333), (1024, 3072, 4096)])
+@pytest.mark.parametrize("n", [1, 8, 9, 33, 64, 100, 300])
+@pytest.mark.parametrize("hidden,inner,width2", [(72, 136, 40), (1000, 2048, 333), (1024, 3072, 4096), (2304, 1024, 520)])
 @pytest.mark.parametrize("epilogue", ["none", "silu_gate"])
 @pytest.mark.parametrize("gdt", [torch.bfloat16, torch.float32])
 def test_linear_with_a_folded_norm(K, n, hidden, inner, width2, epilogue, gdt, monkeypatch):
+    monkeypatch.setattr(K, "fold_max_rows", 64)
+    monkeypatch.setattr(K, "tc_fold_max_rows", 1 << 20)
+    _folded_norm_case(K, n, hidden, inner, width2, epilogue, gdt)
+
+
+def test_linear_with_a_folded_norm_on_wide_tiles(K, monkeypatch):
+    """The same where the first product has enough rows and features for tiles of 256 x 256."""
+    monkeypatch.setattr(K, "tc_fold_max_rows", 1 << 20)
+    _folded_norm_case(K, 1300, 4096, 512, 256, "none", torch.bfloat16)
+    _folded_norm_case(K, 1300, 4096, 512, 256, "silu_gate", torch.float32)
+
+
+def _folded_norm_case(K, n, hidden, inner, width2, epilogue, gdt):
     """x += a w1^T, RMSNorm, then a second product, with the norm done by the two products: the
     first writes x * g and partial sums of squares, the second multiplies its rows by the factor.
-    Against the three steps done one after the other in float64.  (The engine folds up to
-    fold_max_rows rows; the kernels take as many as the few-rows product does.)"""
-    monkeypatch.setattr(K, "fold_max_rows", 64)
+    Against the three steps done one after the other in float64.  The row counts and sizes reach
+    the few-rows kernel and the tcgen05 kernel in its forms (one tile per CTA narrow and wide, the
+    k range shared by a cluster, the persistent one for the second product), on either side.  (The
+    engine folds up to fold_max_rows rows on the few-rows kernel; it takes as many as that product does.)"""
     a = rnd((n, inner), torch.bfloat16, 1)
     w1 = rnd((hidden, inner), torch.bfloat16, 2, scale=inner ** -0.5)
     x = rnd((n, hidden), torch.float32, 3)
@@ -444,30 +458,53 @@ def test_linear_with_a_folded_norm(K, n, hidden, inner, width2, epilogue, gdt, m
     x_ref = x.double() + a.double() @ w1.double().t()
     r = torch.rsqrt((x_ref ** 2).mean(dim=1, keepdim=True) + eps)
     xg = (x_ref * g.double()).to(torch.bfloat16)           # what the first product hands over
-    ref = torch.empty((n, width2), dtype=torch.float64)
-    REF.linear((xg.double() * r).to(torch.float64), w2, ref, epilogue)
-    if not K.can_fold_norm(n, torch.bfloat16, w2.cuda()):
-        assert K._on_tcgen05(n, w2.cuda())
-        pytest.skip("a product of this size runs on the tcgen05 kernel, which takes no folded norm")
-    assert K.can_fold_norm(n, torch.bfloat16, w1.cuda())
-    parts = K.fold_parts(hidden)
-    assert parts == -(-hidden // 16)
+    w1d, w2d = w1.cuda(), w2.cuda()
+    assert K.can_fold_norm(n, torch.bfloat16, w2d, epilogue) and K.can_fold_norm(n, torch.bfloat16, w1d)
+    parts = K.fold_parts(hidden, n, w1d)
+    if not K._on_tcgen05(n, w1d):
+        assert parts == -(-hidden // 16)
     xd = x.cuda()
     vals = torch.full((n, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
     partials = torch.full((parts, n), float("nan"), dtype=torch.float32, device="cuda")
-    K.linear_residual_norm(a.cuda(), w1.cuda(), xd, g.cuda(), vals, partials)
-    torch.testing.assert_close(xd.cpu().double(), x_ref, rtol=1e-5, atol=1e-5)
+    K.linear_residual_norm(a.cuda(), w1d, xd, g.cuda(), vals, partials)
+    # the few-rows kernel adds k in float32 registers; the tcgen05 accumulator is held to what its plain product is
+    tol = dict(rtol=2e-4, atol=1e-4) if K._on_tcgen05(n, w1d) else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(xd.cpu().double(), x_ref, **tol)
     torch.testing.assert_close(partials.sum(dim=0).cpu().double(), (x_ref ** 2).sum(dim=1), rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(vals.cpu().float(), xg.float(), rtol=1e-2, atol=1e-3)
+    # the second product is held to the values that were handed over (they may differ from xg in a last bfloat16 bit)
+    ref = torch.empty((n, width2), dtype=torch.float64)
+    REF.linear(vals.cpu().double() * r, w2, ref, epilogue)
     for od in (torch.bfloat16, torch.float32):
         out = torch.full((n, width2), float("nan"), dtype=od, device="cuda")
-        K.linear(vals, w2.cuda(), out, epilogue, row_scale=(partials, parts, eps, hidden))
+        K.linear(vals, w2d, out, epilogue, row_scale=(partials, parts, eps, hidden))
         torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2 if od == torch.bfloat16 else 4e-3,
                                    atol=4e-3 if od == torch.bfloat16 else 2e-3)
-    with pytest.raises(Exception):                          # many rows: no folded norm
-        big = torch.zeros((200, hidden), dtype=torch.bfloat16, device="cuda")
-        K.linear(big, w2.cuda(), torch.empty((200, width2), dtype=torch.bfloat16, device="cuda"), epilogue,
-                 row_scale=(torch.zeros((parts, 200), device="cuda"), parts, eps, hidden))
+    K.check_device_errors()
+    if n > 64 and hidden % 8:                               # many rows on the plain kernel: no folded norm
+        assert not K.can_fold_norm(n, torch.float32, w2d.float(), epilogue)
+
+
+@pytest.mark.parametrize("n,o,k,splits", [(1, 128, 1024, 2), (9, 1024, 2048, 8), (64, 1000, 1096, 3), (128, 384, 4096, 5),
+                                          (100, 72, 136, 2), (5, 200, 136, 8), (37, 4096, 12288, 4)])
+@pytest.mark.parametrize("od", [torch.bfloat16, torch.float32])
+def test_linear_tcgen05_with_a_shared_k_range(K, n, o, k, splits, od):
+    """The tcgen05 product whose tiles' k range is shared by a cluster of CTAs: every cluster size class, a k range
+    that does not divide (a CTA with fewer k blocks, one with none), features and rows that leave the tiles ragged;
+    twice, with the same bits (the parts are added in a fixed order)."""
+    x = rnd((n, k), torch.bfloat16, 4)
+    w = rnd((o, k), torch.bfloat16, 5, scale=k ** -0.5)
+    ref = torch.empty((n, o), dtype=od)
+    REF.linear(x, w, ref, "none")
+    outs = []
+    for _ in range(2):
+        out = torch.full((n, o), float("nan"), dtype=od, device="cuda")
+        K._linear_tcgen05_split(x.cuda(), w.cuda(), out, n, o, k, splits)
+        outs.append(out.cpu())
+    K.check_device_errors()
+    assert torch.equal(outs[0], outs[1])
+    torch.testing.assert_close(outs[0].float(), ref.float(), rtol=1.6e-2 if od == torch.bfloat16 else 2e-4,
+                               atol=2e-3 if od == torch.bfloat16 else 1e-4)
 
 
 @pytest.mark.parametrize("od", [torch.bfloat16, torch.float32])

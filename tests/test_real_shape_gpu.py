@@ -73,8 +73,8 @@ def test_real_layer_sizes(model, dtype, tolerance):
 # ----------------------------------------------------------------------------------------------------------------
 # Every way of cutting the work where the product's own kernels meet: head size 128 and pages of 16, so that prompt
 # portions run on the tcgen05 attention kernel beside decoded tokens on the TMA-fed small-q kernel in one step,
-# products of more than 64 rows on tcgen05 beside few-row ones, norms folded into products below 33 rows and run as
-# kernels above.  The layer sizes are Qwen3-0.6B's, with two layers and a vocabulary of 4,096.
+# products of more than 64 rows on tcgen05 beside few-row ones (and, from 17 rows, o and down on tcgen05 with their k
+# range shared by a cluster), norms folded into the products of steps up to 128 rows and run as kernels above.  The layer sizes are Qwen3-0.6B's, with two layers and a vocabulary of 4,096.
 # ----------------------------------------------------------------------------------------------------------------
 CUT_LENS = [137, 300, 64, 19, 285, 150, 1, 2, 328]
 
@@ -115,7 +115,7 @@ def test_cutting_modes_at_the_real_head_size(small_06b, mode, dtype, tolerance):
     opts = EngineOptions(dtype=dtype, page_size=16, num_pages=1024 // 16, max_num_seqs=4, max_num_batched_tokens=1024)
     runner = build_runner(path, opts)[2]
     K = runner.rt.kernels
-    before = (K.tc_attention_calls, K.small_q_tma_calls, K.fused_qkv_calls)
+    before = (K.tc_attention_calls, K.small_q_tma_calls, K.fused_qkv_calls, K.tc_shared_k_calls, K.tc_folded_calls)
     out = tiny.collect(steps, tiny.run_inprocess(runner, steps), cfg["vocab_size"])
     runner.cache.check()
     assert runner.cache.free_pages() == [64]
@@ -136,6 +136,9 @@ def test_cutting_modes_at_the_real_head_size(small_06b, mode, dtype, tolerance):
         if mode != "whole":
             assert K.small_q_tma_calls > before[1], "the TMA-fed small-q kernel did not run"
             assert K.fused_qkv_calls > before[2], "the q | k | v product with norm, rotation and store in its epilogue did not run"
+        if mode in ("portions", "mixed"):          # steps of some tens of tokens
+            assert K.tc_shared_k_calls > before[3], "no tcgen05 product shared its k range in a cluster"
+            assert K.tc_folded_calls > before[4], "no tcgen05 product took or made a folded norm"
     K.check_device_errors()
 
 
