@@ -154,6 +154,18 @@ struct TcFold {
   const void* res_g;          // [o_out] norm weight
   int res_g_dtype;
   float* res_partials;        // [parts][n_rows], written; what a part covers depends on the launch (tc_fold_parts)
+  // The product is the fused q | k | v projection of an attention layer with heads of 128, in the shared-k form, whose
+  // tile of 128 features is one head: the sum over the cluster finishes what follows the projection (RMSNorm over the q
+  // and k heads, rotation in the half-split pairing, q to its row, k and v to the token's place in the pages).
+  int qk_nq, qk_nkv;          // qk_nq > 0: on
+  const void* qk_qw;          // [128] norm weights (null: no norm)
+  const void* qk_kw;
+  int qk_w_dtype;
+  float qk_eps;
+  const float2* qk_rope;      // [n_rows][64] (cos, sin) of each token's angles (null: no rotation)
+  const int* qk_slots;        // [n_rows] page * page_size + offset, negative: store nothing (null: no store)
+  bf16* qk_pages;             // [page][k | v][kv head][offset][128]
+  int qk_page_size;
 };
 __device__ __forceinline__ float tc_row_factor(const TcFold& f, int row, int n_rows) {
   if (!f.rs_partials || row >= n_rows) return 1.f;
@@ -215,7 +227,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   const int kb_per = (kb_all + splits - 1) / splits;
   const int kb0 = blockIdx.z * kb_per;
   const int kblocks = max(0, min(kb_all, kb0 + kb_per) - kb0);    // this CTA's k blocks are kb0 .. kb0 + kblocks - 1
-  constexpr int RED_PITCH = FO + 4;                               // floats per row of the tile left in shared memory
+  constexpr int RED_PITCH = NACC + 4;                             // floats per row of the tile left in shared memory
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -320,6 +332,25 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           uint32_t v[32];
           float y[32];
           tmem_ld32(lane_base + c0, v);
+          if (splits > 1) {
+            // the part stays here for the cluster's sum (with the silu_gate epilogue: the gate columns, then the up
+            // columns FO further on; the epilogue itself comes after the sum)
+            float* dst = reinterpret_cast<float*>(smem) + (size_t)(hf * G_BM + q * 32 + lane) * RED_PITCH + c0;
+            uint32_t u[32];
+            if (EPI) tmem_ld32(lane_base + FO + c0, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]) * rfac, __uint_as_float(v[j + 1]) * rfac,
+                                                                __uint_as_float(v[j + 2]) * rfac, __uint_as_float(v[j + 3]) * rfac);
+            if (EPI) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + FO + j) = make_float4(__uint_as_float(u[j]) * rfac, __uint_as_float(u[j + 1]) * rfac,
+                                                                       __uint_as_float(u[j + 2]) * rfac, __uint_as_float(u[j + 3]) * rfac);
+            }
+            continue;
+          }
           if (EPI) {
             uint32_t u[32];
             tmem_ld32(lane_base + FO + c0, u);
@@ -336,13 +367,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 #pragma unroll
             for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]) * rfac;
           }
-          if (!EPI && splits == 1 && fold.res_x) ss += tc_residual_chunk(fold, y, row0 + lane, n_rows, n0 + c0, o_out);
-          if (splits > 1) {                                      // the part stays here for the cluster's sum
-            float* dst = reinterpret_cast<float*>(smem) + (size_t)(hf * G_BM + q * 32 + lane) * RED_PITCH + c0;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
-            continue;
-          }
+          if (!EPI && fold.res_x) ss += tc_residual_chunk(fold, y, row0 + lane, n_rows, n0 + c0, o_out);
           if (vec) {
             unsigned char* dst = buf + lane * PITCH + (c0 - p0) * (int)sizeof(TO);
             if (sizeof(TO) == 2) {
@@ -386,7 +411,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   }
   if (splits > 1) {
     cluster_sync_all();                        // every CTA's part is in its shared memory
-    if (fold.res_x) ifb_pdl_wait();
+    if (fold.res_x || fold.qk_nq) ifb_pdl_wait();
     const int rows = min(G_BM, n_rows - m0), cols = min(FO, o_out - n0);
     const int used = (kb_all + kb_per - 1) / kb_per;                       // CTAs that had k blocks
     const int per = (rows + splits - 1) / splits;
@@ -401,8 +426,19 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         const float4 v = ld_cluster_f4(at, z);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
       }
+      if (EPI) {
+        float4 up = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z = 0; z < used; ++z) {
+          const float4 v = ld_cluster_f4(at + FO * 4, z);
+          up.x += v.x; up.y += v.y; up.z += v.z; up.w += v.w;
+        }
+        acc.x = acc.x * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * acc.x)) * up.x;
+        acc.y = acc.y * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * acc.y)) * up.y;
+        acc.z = acc.z * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * acc.z)) * up.z;
+        acc.w = acc.w * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * acc.w)) * up.w;
+      }
       TO* dst = out + (size_t)(m0 + r) * o_out + n0 + c;
-      if (fold.res_x) {
+      if (!EPI && fold.res_x) {
         // a warp holds one row of the tile: v = x + y, x <- v, the output becomes v * g, the warp's sum of v^2 one part
         float* xr = fold.res_x + (size_t)(m0 + r) * o_out + n0 + c;
         float yv[4] = {acc.x, acc.y, acc.z, acc.w}, ss = 0.f;
@@ -418,6 +454,42 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
         if ((threadIdx.x & 31) == 0) fold.res_partials[(size_t)blockIdx.x * n_rows + m0 + r] = ss;
         acc = make_float4(yv[0], yv[1], yv[2], yv[3]);
+      }
+      if (!EPI && sizeof(TO) == 2 && fold.qk_nq) {
+        // a warp holds one head of one token (lane l its elements 4l .. 4l + 3; the rotation partner 16 lanes on)
+        const int head = blockIdx.x, ln = threadIdx.x & 31;
+        const bool is_v = head >= fold.qk_nq + fold.qk_nkv, is_k = head >= fold.qk_nq && !is_v;
+        float yv[4] = {acc.x, acc.y, acc.z, acc.w};
+        const void* wn = is_k ? fold.qk_kw : fold.qk_qw;
+        if (!is_v && wn) {
+          float ss = yv[0] * yv[0] + yv[1] * yv[1] + yv[2] * yv[2] + yv[3] * yv[3];
+#pragma unroll
+          for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+          const float rn = rsqrtf(ss * (1.f / 128.f) + fold.qk_eps);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) yv[j] = yv[j] * rn * load_as_f32(wn, fold.qk_w_dtype, c + j);
+        }
+        if (!is_v && fold.qk_rope) {
+          const float2* t = fold.qk_rope + (size_t)(m0 + r) * 64 + (c & 63);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float o = __shfl_xor_sync(0xffffffffu, yv[j], 16);
+            const float2 cs = t[j];
+            yv[j] = ln < 16 ? yv[j] * cs.x - o * cs.y : yv[j] * cs.x + o * cs.y;
+          }
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(yv[0], yv[1]), hi = __floats2bfloat162_rn(yv[2], yv[3]);
+        const uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        *reinterpret_cast<uint2*>(dst) = pk;
+        if (head >= fold.qk_nq && fold.qk_slots) {
+          const int slot = fold.qk_slots[m0 + r];
+          if (slot >= 0) {
+            const int kvh = is_v ? head - fold.qk_nq - fold.qk_nkv : head - fold.qk_nq;
+            const size_t row = ((size_t)(slot / fold.qk_page_size) * 2 + (is_v ? 1 : 0)) * fold.qk_nkv + kvh;
+            *reinterpret_cast<uint2*>(fold.qk_pages + (row * fold.qk_page_size + slot % fold.qk_page_size) * 128 + c) = pk;
+          }
+        }
+        continue;
       }
       if (vec) {
         if (sizeof(TO) == 4) {
@@ -752,10 +824,11 @@ static int tc_launch(const void* x, const void* w, void* out, int n, int o, int 
   using P128 = PersistCfg<EPI, EPI ? 256 : 128, EPI ? 3 : 5>;      // 128 features per tile
   using P256 = PersistCfg<EPI, 256, 3>;                            // 256 features per tile (plain epilogue only)
   if (splits > 1) {
-    static_assert(G_BM * (Deep::FO + 4) * 4 <= Narrow::STAGES * Narrow::STAGE_BYTES, "the float32 tile must fit in the stages");
-    if (EPI || splits > 8) return IFB_ERR_ARG;
+    static_assert(G_BM * (Deep::NACC + 4) * 4 <= Deep::STAGES * Deep::STAGE_BYTES, "the float32 tile must fit in the stages");
+    if (splits > 8) return IFB_ERR_ARG;
     // one tile of rows: a CTA per SM with a deep ring; more: two CTAs per SM, one's sum beside the other's products
-    if (n <= G_BM && shape != 1) return tc_launch_cfg<Deep, TO>(x, w, out, n, o, k, err, s, fold, splits);
+    if ((n <= G_BM && shape != 1) || G_BM * (Narrow::NACC + 4) * 4 > Narrow::STAGES * Narrow::STAGE_BYTES)
+      return tc_launch_cfg<Deep, TO>(x, w, out, n, o, k, err, s, fold, splits);
     return tc_launch_cfg<Narrow, TO>(x, w, out, n, o, k, err, s, fold, splits);
   }
   if (shape == 0) shape = tc_pick_shape(EPI, n, o);
@@ -770,7 +843,7 @@ static int tc_launch(const void* x, const void* w, void* out, int n, int o, int 
 // x [n_rows, k] and w [out_features (x2 for the silu_gate epilogue), k] bfloat16, 16-byte aligned, k a multiple of 8;
 // out bfloat16 or float32.  `err` points to a device int that stays 0 unless a bounded wait gave up.  shape: 0 lets the
 // library choose, 1-3 force the one-tile-per-CTA kernel narrow, deep or wide, 4 and 5 the persistent kernel with tiles
-// of 128 or 256 features.  splits 2 to 8 (plain epilogue): the k range of a tile of 128 x 128 is shared by a cluster of
+// of 128 or 256 features.  splits 2 to 8: the k range of a tile of 128 x 128 is shared by a cluster of
 // that many CTAs, whose parts are added in a fixed order; for few tiles of a long k (a step of some tens of tokens).
 // scale_partials (may be null): [scale_parts][n_rows] sums of squares; output row n is multiplied by
 // rsqrt(sum_p partials[p][n] / scale_width + scale_eps) before the epilogue.
@@ -787,8 +860,10 @@ IFB_EXPORT int ifb_linear_tcgen05_ex(const void* x, const void* w, void* out, in
   if (shape < 0 || shape > 5 || splits < 0 || splits > 8) return IFB_ERR_ARG;
   if (scale_partials && (scale_parts < 1 || scale_width < 1)) return IFB_ERR_ARG;
   if (res_x && (!res_g || !res_partials || ((uintptr_t)res_x & 15))) return IFB_ERR_ARG;
-  const TcFold fold{scale_partials, scale_parts, scale_eps, scale_partials ? 1.f / (float)scale_width : 0.f,
-                    res_x, res_g, res_g_dtype, res_partials};
+  TcFold fold = {};
+  fold.rs_partials = scale_partials; fold.rs_parts = scale_parts; fold.rs_eps = scale_eps;
+  fold.rs_inv_width = scale_partials ? 1.f / (float)scale_width : 0.f;
+  fold.res_x = res_x; fold.res_g = res_g; fold.res_g_dtype = res_g_dtype; fold.res_partials = res_partials;
   if (out_dtype == IFB_BF16)
     return epilogue ? tc_launch<1, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream)
                     : tc_launch<0, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream);
@@ -802,6 +877,31 @@ IFB_EXPORT int ifb_linear_tcgen05(const void* x, const void* w, void* out, int o
                                   int k_dim, int epilogue, int* err, int shape, cudaStream_t stream) {
   return ifb_linear_tcgen05_ex(x, w, out, out_dtype, n_rows, out_features, k_dim, epilogue, shape, 1, nullptr, 0, 0.f, 0, nullptr,
                                nullptr, 0, nullptr, err, stream);
+}
+
+// The fused q | k | v projection of an attention layer in the shared-k form with what follows it in the sum over the
+// cluster (see TcFold): qkv [n_rows, (nq + 2 nkv) * 128] bfloat16 gets the normalised and rotated q heads (and the k and
+// v heads as they are stored), the pages get k and v at slots[n].  Heads of 128, rotated whole in the half-split pairing
+// (rope: [n_rows][64] pairs of cos and sin, or null); splits 2 to 8.  scale_*: as in ifb_linear_tcgen05_ex.
+IFB_EXPORT int ifb_linear_tcgen05_qkv(const void* x, const void* w, void* qkv, int n_rows, int nq, int nkv, int head_dim, int k_dim,
+                                      int splits, const float* scale_partials, int scale_parts, float scale_eps, int scale_width,
+                                      const void* q_weight, const void* k_weight, int w_dtype, float eps, const float* rope,
+                                      const int* slots, void* pages, int page_size, int* err, cudaStream_t stream) {
+  if (n_rows <= 0) return IFB_OK;
+  if (head_dim != 128 || nq < 1 || nkv < 1 || splits < 2 || splits > 8) return IFB_ERR_SIZE;
+  if (k_dim < 8 || k_dim % 8) return IFB_ERR_SIZE;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)qkv & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)rope & 7))
+    return IFB_ERR_ALIGN;
+  if ((q_weight || k_weight) && w_dtype != IFB_F32 && w_dtype != IFB_BF16) return IFB_ERR_DTYPE;
+  if (scale_partials && (scale_parts < 1 || scale_width < 1)) return IFB_ERR_ARG;
+  if (slots && (!pages || page_size < 1)) return IFB_ERR_ARG;
+  TcFold fold = {};
+  fold.rs_partials = scale_partials; fold.rs_parts = scale_parts; fold.rs_eps = scale_eps;
+  fold.rs_inv_width = scale_partials ? 1.f / (float)scale_width : 0.f;
+  fold.qk_nq = nq; fold.qk_nkv = nkv; fold.qk_qw = q_weight; fold.qk_kw = k_weight; fold.qk_w_dtype = w_dtype; fold.qk_eps = eps;
+  fold.qk_rope = reinterpret_cast<const float2*>(rope); fold.qk_slots = slots; fold.qk_pages = (bf16*)pages;
+  fold.qk_page_size = page_size;
+  return tc_launch<0, bf16>(x, w, qkv, n_rows, (nq + 2 * nkv) * 128, k_dim, err, 0, splits, fold, stream);
 }
 
 // Parts of sums of squares that a product with res_x writes per row (the launch with shape 0 and these splits).

@@ -110,7 +110,8 @@ class CudaKernels:
         self.tc_folded_calls = 0
         self._err_armed = False
         self.tc_min_rows = 65
-        self.tc_split_min_k = int(os.environ.get("INFURNACE_TC_SPLIT_MIN_K", "512"))
+        self.tc_split_min_k = int(os.environ.get("INFURNACE_TC_SPLIT_MIN_K", "256"))
+        self.fused_qkv_tc = os.environ.get("INFURNACE_FUSED_QKV_TC", "1") != "0"
         self.tc_split_min_rows = int(os.environ.get("INFURNACE_TC_SPLIT_MIN_ROWS", "0"))     # 0: by the matrix
         self.tc_fold_max_rows = int(os.environ.get("INFURNACE_TC_FOLD_MAX_ROWS", "128"))
         self._tc_clusters = {}         # CTAs per cluster -> clusters of the split product that run at a time
@@ -195,8 +196,8 @@ class CudaKernels:
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 \
                 and out.dtype in (torch.bfloat16, torch.float32):
             if self._on_tcgen05(n, w, epilogue):
-                splits = self.tcgen05_splits(n, o, k) if not epi else 1
-                return self._linear_tcgen05(x, w, out, n, o, k, epi, splits=splits, row_scale=row_scale)
+                return self._linear_tcgen05(x, w, out, n, o, k, epi, splits=self.tcgen05_splits(n, o, k, epi),
+                                            row_scale=row_scale)
             return self._linear_gemv(x, w, out, n, o, k, epi, row_scale)
         self.launches += 1
         _check(self.core.ifb_linear_simt(x.data_ptr(), _code(x), w.data_ptr(), _code(w), out.data_ptr(), _code(out),
@@ -257,13 +258,16 @@ class CudaKernels:
                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
             self._tc.ifb_linear_tcgen05_split_clusters.argtypes = [c_int]
             self._tc.ifb_linear_tcgen05_fold_parts.argtypes = [c_int, c_int, c_int]
+            self._tc.ifb_linear_tcgen05_qkv.argtypes = [
+                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_int,
+                c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
         return self._tc
 
-    def tcgen05_splits(self, n, o, k):
-        """How many CTAs (a cluster) share the k range of a tile in the tcgen05 product of up to 512 rows:
-        the most, up to 8, whose clusters for all tiles of 128 x 128 run at the same time, each CTA
-        with at least ``tc_split_min_k`` of k; 1 if that is none."""
-        if n > 512:
+    def tcgen05_splits(self, n, o, k, epi=0):
+        """How many CTAs (a cluster) share the k range of a tile in the tcgen05 product of up to 512 rows
+        (128 with the silu_gate epilogue): the most, up to 8, whose clusters for all tiles of 128 x 128
+        run at the same time, each CTA with at least ``tc_split_min_k`` of k; 1 if that is none."""
+        if n > (128 if epi else 512):
             return 1
         tiles = -(-o // 128) * -(-n // 128)
         for splits in range(min(8, k // self.tc_split_min_k), 1, -1):
@@ -373,12 +377,23 @@ class CudaKernels:
 
     # The q | k | v projection of a decode step with the head norm, the rotation and the page store in its epilogue.
     def can_fuse_qkv(self, n, dtype, w_qkv, head_dim, rotary_dim, interleaved, kv_pages):
-        """Whether :meth:`linear_qkv_rope_store` takes a step of ``n`` rows: few rows of bfloat16 on the few-rows
-        kernel, heads of 64, 128 or 256 rotated whole in the half-split pairing (or not rotated)."""
-        return (self.fused_qkv and 0 < n <= 16 and dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
-                and w_qkv.shape[1] % 8 == 0 and head_dim in (64, 128, 256) and not self._on_tcgen05(n, w_qkv, shared_k=False)
-                and (rotary_dim == 0 or (rotary_dim == head_dim and not interleaved))
-                and (kv_pages is None or kv_pages.dtype == torch.bfloat16))
+        """Whether :meth:`linear_qkv_rope_store` takes a step of ``n`` rows: bfloat16, heads rotated whole in
+        the half-split pairing (or not rotated); up to 16 rows on the few-rows kernel (heads of 64, 128 or
+        256), or up to 128 rows on the tcgen05 kernel in its shared-k form (heads of 128)."""
+        if not (self.fused_qkv and n > 0 and dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
+                and w_qkv.shape[1] % 8 == 0 and (rotary_dim == 0 or (rotary_dim == head_dim and not interleaved))
+                and (kv_pages is None or kv_pages.dtype == torch.bfloat16)):
+            return False
+        return self._fused_qkv_route(n, w_qkv, head_dim) is not None
+
+    def _fused_qkv_route(self, n, w_qkv, head_dim):
+        """"gemv", "tcgen05" or None for the fused q | k | v product of ``n`` rows."""
+        if n <= 16 and head_dim in (64, 128, 256) and not self._on_tcgen05(n, w_qkv, shared_k=False):
+            return "gemv"
+        if n <= 128 and head_dim == 128 and self.fused_qkv_tc and self._on_tcgen05(n, w_qkv) \
+                and self.tcgen05_splits(n, w_qkv.shape[0], w_qkv.shape[1]) > 1:
+            return "tcgen05"
+        return None
 
     def linear_qkv_rope_store(self, x, w_qkv, qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, rope_table,
                               slot_mapping, kv_pages, row_scale=None):
@@ -412,6 +427,20 @@ class CudaKernels:
         partials, parts, seps, swidth = row_scale if row_scale is not None else (None, 0, 0.0, 0)
         self.launches += 1
         self.fused_qkv_calls += 1
+        route = self._fused_qkv_route(n, w_qkv, head_dim)
+        if route is None:
+            raise KernelError("linear_qkv_rope_store: no kernel takes these sizes (see can_fuse_qkv)")
+        if route == "tcgen05":
+            self._err_armed = True
+            self.tc_shared_k_calls += 1
+            self.tc_folded_calls += partials is not None
+            _check(self._tc_lib().ifb_linear_tcgen05_qkv(
+                x.data_ptr(), w_qkv.data_ptr(), qkv.data_ptr(), n, num_heads, num_kv_heads, head_dim, k,
+                self.tcgen05_splits(n, width, k), _ptr(partials), int(parts), float(seps), int(swidth), _ptr(q_weight),
+                _ptr(k_weight), wd, float(eps), _ptr(rope_table), _ptr(slot_mapping),
+                _ptr(kv_pages) if slot_mapping is not None else 0, page_size, self._dev_err.data_ptr(), self._stream()),
+                "linear_qkv_rope_store")
+            return
         _check(self.core.ifb_linear_gemv_qkv(
             x.data_ptr(), w_qkv.data_ptr(), qkv.data_ptr(), n, num_heads, num_kv_heads, head_dim, k, _ptr(partials),
             int(parts), float(seps), int(swidth), _ptr(q_weight), _ptr(k_weight), wd, float(eps), _ptr(rope_table),

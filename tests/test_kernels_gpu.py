@@ -193,21 +193,30 @@ def test_qk_norm_rope_store_for_many_tokens_of_head_size_128(K, nq, nkv, ps, nor
     assert kv_gpu.cpu()[kv_ref == 0].abs().max() == 0
 
 
-@pytest.mark.parametrize("n", [1, 5, 8, 13, 16])
-@pytest.mark.parametrize("nq,nkv,d,k,ps", [(16, 8, 128, 1024, 16), (4, 2, 64, 2048, 8), (2, 1, 256, 4096, 32), (3, 3, 128, 136, 16)])
+@pytest.mark.parametrize("n", [1, 5, 8, 13, 16, 40, 100, 128])
+@pytest.mark.parametrize("nq,nkv,d,k,ps", [(16, 8, 128, 1024, 16), (4, 2, 64, 2048, 8), (2, 1, 256, 4096, 32), (3, 3, 128, 136, 16),
+                                           (5, 1, 128, 2056, 32)])
 @pytest.mark.parametrize("norm,rotate,scaled", [(True, True, False), (True, True, True), (False, True, False), (True, False, False)])
 def test_qkv_product_with_norm_rotation_and_store_in_its_epilogue(K, n, nq, nkv, d, k, ps, norm, rotate, scaled):
-    """The one-launch form of a decode step's q | k | v projection against its three steps in float64: the
+    """The one-launch form of a step's q | k | v projection against its three steps in float64: the
     product (with the row factors of a folded norm before it, when ``scaled``), the RMSNorm of the q and k
-    heads, the rotation, and k and v in the pages at the tokens' slots (one token stores nothing)."""
+    heads, the rotation, and k and v in the pages at the tokens' slots (one token stores nothing).  Up to 16
+    rows on the few-rows kernel (a cluster per head), more rows of heads of 128 on the tcgen05 kernel whose
+    clusters share the k range of a head."""
     width = (nq + 2 * nkv) * d
+    if n > 16:
+        w_probe = torch.empty((width, k), dtype=torch.bfloat16, device="cuda")
+        can = K.can_fuse_qkv(n, torch.bfloat16, w_probe, d, d if rotate else 0, False, None)
+        assert can == (d == 128 and k >= 512), "heads of 128 with enough of k for two CTAs run fused on tcgen05"
+        if not can:
+            pytest.skip("more than 16 rows run fused only with heads of 128 on tcgen05")
     x = rnd((n, k), torch.bfloat16, 1)
     w = rnd((width, k), torch.bfloat16, 2, scale=k ** -0.5)
     qw = (1 + 0.1 * rnd((d,), torch.float32, 3)).to(torch.bfloat16) if norm else None
     kw = (1 + 0.1 * rnd((d,), torch.float32, 4)) if norm else None          # float32 beside bfloat16 is refused below
     positions = torch.randint(0, 5000, (n,), dtype=torch.int32)
     inv_freq = 1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
-    pages = 7
+    pages = max(7, -(-n // ps) + 1)
     slots = torch.randperm(pages * ps)[:n].to(torch.int32)
     if n > 2:
         slots[2] = -1
