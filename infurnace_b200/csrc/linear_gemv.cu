@@ -75,13 +75,15 @@ __device__ __forceinline__ void gv_cluster_barrier() {
 }
 
 // NB: blocks of 8 tokens per CTA.  EPI 0: out = y.  EPI 1: w holds gate rows [0, O) and up rows [O, 2O);
-// out = silu(gate) * up.  EPI 2: v = x + y is written back to x, out = v * g.  WARPS: warps of a CTA (they split k).
+// out = silu(gate) * up.  EPI 2: v = x + y is written back to x, out = v * g.  EPI 4: as EPI 1 with 8 features per
+// CTA, whose 8 gate rows and 8 up rows are the two halves of one 16-row tile (half the registers of EPI 1, so two CTAs
+// per SM where EPI 1 with two stages has one).  WARPS: warps of a CTA (they split k).
 // STAGES: steps of 128 of k whose weights (and, for one block of tokens, activations) a warp has requested at any
 // time.  1: every warp's k range is one step (the sizes of small models, where the chain of round trips counts);
 // 2: a warp walks a long k range and keeps the memory pipe full while it multiplies (large models, where the
 // bytes count).
 template <int NB, int EPI, int WARPS, typename TO, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, (EPI == 4 && WARPS == 8) ? 2 : 1)
 linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* __restrict__ out, int n_rows, int o_out,
                    int k_dim, GvRowScale rs, GvResidual res, GvQkv qk) {
   extern __shared__ float gv_red[];                 // [WARPS][NE][NB*8][GV_ROWS], then [NB*8] row factors
@@ -94,16 +96,20 @@ linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* _
   // their rotation partners head_dim/2 further on
   const int qk_per_head = EPI == 3 ? qk.head_dim / 32 : 1;
   const int qk_head = EPI == 3 ? blockIdx.x / qk_per_head : 0, qk_c = EPI == 3 ? blockIdx.x % qk_per_head : 0;
-  const int o0 = EPI == 3 ? qk_head * qk.head_dim + qk_c * GV_ROWS : blockIdx.x * GV_ROWS, n0 = blockIdx.y * (NB * 8);
+  const int o0 = EPI == 3 ? qk_head * qk.head_dim + qk_c * GV_ROWS : blockIdx.x * (EPI == 4 ? 8 : GV_ROWS), n0 = blockIdx.y * (NB * 8);
   const int second = EPI == 3 ? qk.head_dim / 2 : o_out;      // distance of the second set of 16 weight rows from the first
   const int kw = ((k_dim + WARPS - 1) / WARPS + 127) / 128 * 128;      // k per warp, whole 128-wide steps
   const int kbeg = warp * kw, kend = min(k_dim, kbeg + kw);
-  const int w_rows = EPI == 1 ? 2 * o_out : o_out;
+  const int w_rows = (EPI == 1 || EPI == 4) ? 2 * o_out : o_out;
   const bf16* wrow[NE][2];
 #pragma unroll
   for (int e = 0; e < NE; ++e) {
     wrow[e][0] = w + (size_t)min(e * second + o0 + rr, w_rows - 1) * k_dim;
     wrow[e][1] = w + (size_t)min(e * second + o0 + rr + 8, w_rows - 1) * k_dim;
+  }
+  if (EPI == 4) {                                               // rows 0-7 of the tile: gate; rows 8-15: up of the same features
+    wrow[0][0] = w + (size_t)min(o0 + rr, o_out - 1) * k_dim;
+    wrow[0][1] = w + (size_t)min(o_out + o0 + rr, w_rows - 1) * k_dim;
   }
   const bf16* xrow[NB];
   bool xok[NB];
@@ -285,6 +291,15 @@ linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* _
     }
     float r = y[0];
     if (EPI == 1) r = r / (1.f + expf(-r)) * y[NE - 1];
+    if (EPI == 4) {                                    // this item is the gate of feature o0 + m; its up sits 8 rows on
+      if (m >= 8) continue;
+      float up = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < WARPS; ++wv) up += gv_red[((size_t)wv * NB * 8 + n) * GV_ROWS + m + 8];
+      if (rs.partials) up *= row_factor[n];
+      if (valid) out[(size_t)tok * o_out + o] = from_f32<TO>(r / (1.f + expf(-r)) * up);
+      continue;
+    }
     if (EPI == 3) { qk_y0 = y[0]; qk_y1 = y[NE - 1]; continue; }      // finished below, after the loop (one item per thread)
     if (EPI == 2) {
       float v = 0.f;
@@ -356,9 +371,10 @@ static int gv_launch(const void* x, const void* w, void* out, int n, int o, int 
   static_assert(EPI != 3, "the fused qkv epilogue is launched by gv_launch_qkv");
   const size_t smem = ((size_t)WARPS * (EPI == 1 ? 2 : 1) * NB * 8 * GV_ROWS + NB * 8) * sizeof(float);
   IFB_ALLOW_SMEM((linear_gemv_kernel<NB, EPI, WARPS, TO, STAGES>), smem);
-  dim3 grid((o + GV_ROWS - 1) / GV_ROWS, (n + NB * 8 - 1) / (NB * 8));
+  constexpr int PER_CTA = EPI == 4 ? 8 : GV_ROWS;
+  dim3 grid((o + PER_CTA - 1) / PER_CTA, (n + NB * 8 - 1) / (NB * 8));
   // matrices beyond GV_EARLY_BYTES are streamed; a launch ahead of the predecessor's end costs them more than it hides
-  const bool early = (size_t)o * k * (EPI == 1 ? 4 : 2) <= GV_EARLY_BYTES;
+  const bool early = (size_t)o * k * ((EPI == 1 || EPI == 4) ? 4 : 2) <= GV_EARLY_BYTES;
   return ifb_launch_opt(early, linear_gemv_kernel<NB, EPI, WARPS, TO, STAGES>, grid, dim3(WARPS * 32), smem, s, (const bf16*)x,
                         (const bf16*)w, (TO*)out, n, o, k, rs, res, GvQkv{});
 }
@@ -390,25 +406,36 @@ static int gv_launch_qkv(const void* x, const void* w, void* out, int n, int k, 
   return IFB_OK;
 }
 
+static int g_gv_gate_plan = 0;      // a plan (see below) for products with the silu_gate epilogue alone; negative: the
+IFB_EXPORT void ifb_linear_gemv_set_gate_plan(int plan) { g_gv_gate_plan = plan; }      // 16-features-per-CTA form throughout
+
 template <int EPI, int WARPS, typename TO, int STAGES = 1>
 static int gv_by_n(int nb, const void* x, const void* w, void* out, int n, int o, int k, const GvRowScale& rs,
                    const GvResidual& res, cudaStream_t s) {
   switch (nb) {
-    case 1: return gv_launch<1, EPI, WARPS, TO, STAGES>(x, w, out, n, o, k, rs, res, s);
+    // one block of tokens of a long k (two stages): the silu_gate epilogue in its 8-features-per-CTA form, two CTAs per SM
+    // (40 against 35 to 37 us for the 201 MB of the 8B sizes, 90 against 83 to 85 for the 524 MB of the 32B sizes; with more
+    // blocks of tokens it is the slower one, and for a short k it gains in a chain of its own kind but not in the step)
+    case 1:
+      if (g_gv_gate_plan < 0) return gv_launch<1, EPI, WARPS, TO, STAGES>(x, w, out, n, o, k, rs, res, s);
+      return gv_launch<1, ((EPI == 1 && STAGES == 2) ? 4 : EPI), WARPS, TO, STAGES>(x, w, out, n, o, k, rs, res, s);
     case 2: return gv_launch<2, EPI, WARPS, TO, STAGES>(x, w, out, n, o, k, rs, res, s);
     case 4: return gv_launch<4, EPI, WARPS, TO, STAGES>(x, w, out, n, o, k, rs, res, s);
     default: return gv_launch<8, EPI, WARPS, TO, STAGES>(x, w, out, n, o, k, rs, res, s);
   }
 }
 
-// plan 0: chosen from the sizes.  Otherwise warps * 10 + stages, one of 81, 161, 241, 82 (for measurements).
+// plan 0: chosen from the sizes.  Otherwise warps * 10 + stages, one of 81, 161, 241, 82 (for measurements); 83: as 82
+// with the silu_gate epilogue in its 8-features-per-CTA form.
 static int g_gv_plan = 0;
 IFB_EXPORT void ifb_linear_gemv_set_plan(int plan) { g_gv_plan = plan; }
+
 
 template <int EPI, typename TO>
 static int gv_by_k(int nb, const void* x, const void* w, void* out, int n, int o, int k, const GvRowScale& rs,
                    const GvResidual& res, cudaStream_t s) {
   int plan = g_gv_plan;
+  if (plan == 0 && EPI == 1 && g_gv_gate_plan > 0) plan = g_gv_gate_plan;
   if (plan == 0) {
     // 128 of k per warp and step.  Up to k = 3072 every warp's range is one step: 8 warps cover 1024, 16 warps 2048, 24
     // warps 3072 (one or two blocks of tokens; more do not fit the registers of 768 threads).  Beyond that a warp walks
@@ -426,6 +453,7 @@ static int gv_by_k(int nb, const void* x, const void* w, void* out, int n, int o
       if (nb == 2) return gv_launch<2, EPI, 24, TO, 1>(x, w, out, n, o, k, rs, res, s);
       return gv_by_n<EPI, 16, TO, 1>(nb, x, w, out, n, o, k, rs, res, s);
     case 82: return gv_by_n<EPI, 8, TO, 2>(nb, x, w, out, n, o, k, rs, res, s);
+    case 83: return gv_by_n<EPI == 1 ? 4 : EPI, 8, TO, 2>(nb, x, w, out, n, o, k, rs, res, s);
     default: return IFB_ERR_ARG;
   }
 }

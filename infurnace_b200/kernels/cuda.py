@@ -110,6 +110,8 @@ class CudaKernels:
         self.tc_folded_calls = 0
         self._err_armed = False
         self.tc_min_rows = 65
+        if os.environ.get("INFURNACE_GATE_PLAN"):
+            self.core.ifb_linear_gemv_set_gate_plan(int(os.environ["INFURNACE_GATE_PLAN"]))
         self.tc_split_min_k = int(os.environ.get("INFURNACE_TC_SPLIT_MIN_K", "256"))
         self.fused_qkv_tc = os.environ.get("INFURNACE_FUSED_QKV_TC", "1") != "0"
         self.tc_split_min_rows = int(os.environ.get("INFURNACE_TC_SPLIT_MIN_ROWS", "0"))     # 0: by the matrix
