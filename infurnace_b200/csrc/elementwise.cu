@@ -100,40 +100,43 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     store_from_f32(out, out_dtype, (size_t)orow * hidden + h, vbuf[h] * r * load_as_f32(w, w_dtype, h));
 }
 
-// The same with a warp per row and the row in registers, for widths 128 * IT up to 2048: one pass over global
-// memory, a shuffle reduction, no shared memory and no block barrier.
+// The same with a block of 256 threads per row and the row in registers (16 bytes per thread and pass, all passes
+// requested at once), for widths up to 1024 * IT that are a multiple of 4: one pass over global memory and one block
+// barrier.
 template <int IT>
-__global__ void __launch_bounds__(128)
-rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ delta, int num_splits, size_t split_stride,
-                    const void* __restrict__ w, int w_dtype, float eps, void* __restrict__ out, int out_dtype,
-                    const int* __restrict__ rows, int num_out_rows) {
+__global__ void __launch_bounds__(256)
+rmsnorm_block_kernel(float* __restrict__ x, const float* __restrict__ delta, int num_splits, size_t split_stride,
+                     const void* __restrict__ w, int w_dtype, float eps, void* __restrict__ out, int out_dtype,
+                     const int* __restrict__ rows, int hidden) {
+  __shared__ float scratch[33];
   ifb_pdl_wait();
   ifb_pdl_trigger();
-  constexpr int H = 128 * IT;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int orow = blockIdx.x * 4 + warp;
-  if (orow >= num_out_rows) return;
+  const int orow = blockIdx.x;
   const int row = rows ? rows[orow] : orow;
-  float* xr = x + (size_t)row * H;
+  float* xr = x + (size_t)row * hidden;
   float4 v[IT];
   float ss = 0.f;
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
-    const int idx = (it * 32 + lane) * 4;
-    float4 a = *reinterpret_cast<const float4*>(xr + idx);
-    for (int sp = 0; sp < num_splits; ++sp) {
-      const float4 d = *reinterpret_cast<const float4*>(delta + (size_t)sp * split_stride + (size_t)row * H + idx);
-      a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+    const int idx = (it * 256 + threadIdx.x) * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (idx < hidden) {
+      a = *reinterpret_cast<const float4*>(xr + idx);
+      for (int sp = 0; sp < num_splits; ++sp) {
+        const float4 d = *reinterpret_cast<const float4*>(delta + (size_t)sp * split_stride + (size_t)row * hidden + idx);
+        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+      }
+      if (!rows && num_splits) *reinterpret_cast<float4*>(xr + idx) = a;
     }
-    if (!rows && num_splits) *reinterpret_cast<float4*>(xr + idx) = a;
     v[it] = a;
     ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
   }
-  ss = warp_sum(ss);
-  const float r = rsqrtf(ss / (float)H + eps);
+  ss = block_sum(ss, scratch);
+  const float r = rsqrtf(ss / (float)hidden + eps);
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
-    const int idx = (it * 32 + lane) * 4;
+    const int idx = (it * 256 + threadIdx.x) * 4;
+    if (idx >= hidden) break;
     float g0, g1, g2, g3;
     if (w_dtype == IFB_F32) {
       const float4 g = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + idx);
@@ -145,21 +148,21 @@ rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ delta, int 
     }
     const float y0 = v[it].x * r * g0, y1 = v[it].y * r * g1, y2 = v[it].z * r * g2, y3 = v[it].w * r * g3;
     if (out_dtype == IFB_F32) {
-      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)orow * H + idx) = make_float4(y0, y1, y2, y3);
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)orow * hidden + idx) = make_float4(y0, y1, y2, y3);
     } else {
       const __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
       uint2 pk;
       pk.x = *reinterpret_cast<const uint32_t*>(&lo); pk.y = *reinterpret_cast<const uint32_t*>(&hi);
-      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)orow * H + idx) = pk;
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)orow * hidden + idx) = pk;
     }
   }
 }
 
 template <int IT>
-static int rmsnorm_warp_launch(float* x, const float* delta, int num_splits, size_t split_stride, const void* w, int w_dtype,
-                               float eps, void* out, int out_dtype, const int* rows, int num_out_rows, cudaStream_t stream) {
-  return ifb_launch(rmsnorm_warp_kernel<IT>, dim3((num_out_rows + 3) / 4), dim3(128), 0, stream, x, delta, num_splits, split_stride, w,
-                    w_dtype, eps, out, out_dtype, rows, num_out_rows);
+static int rmsnorm_block_launch(float* x, const float* delta, int num_splits, size_t split_stride, const void* w, int w_dtype,
+                                float eps, void* out, int out_dtype, const int* rows, int num_out_rows, int hidden, cudaStream_t stream) {
+  return ifb_launch(rmsnorm_block_kernel<IT>, dim3(num_out_rows), dim3(256), 0, stream, x, delta, num_splits, split_stride, w, w_dtype,
+                    eps, out, out_dtype, rows, hidden);
 }
 
 IFB_EXPORT int ifb_rmsnorm(float* x, const float* delta, int num_splits, long long split_stride, const void* w,
@@ -167,14 +170,15 @@ IFB_EXPORT int ifb_rmsnorm(float* x, const float* delta, int num_splits, long lo
                            int hidden, cudaStream_t stream) {
   if (num_out_rows <= 0) return IFB_OK;
   if ((w_dtype != IFB_F32 && w_dtype != IFB_BF16) || (out_dtype != IFB_F32 && out_dtype != IFB_BF16)) return IFB_ERR_DTYPE;
-  // many rows: a warp per row; few rows (decoding): a block per row is the shorter chain
-  if (num_out_rows >= 64 && hidden % 128 == 0 && hidden <= 2048 && !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) &&
+  // the row in registers where the width allows 16-byte accesses (measured against a warp per row with the row in its
+  // registers, in a chain of its own kind: 1.7 against 4.3 us at 64 rows of 1,024, 7.0 against 10.8 at 2,048 rows; a
+  // warp's eight requests per tensor are too few in flight)
+  if (hidden % 4 == 0 && hidden <= 8192 && !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) &&
       (split_stride % 4) == 0) {
     const int ns = delta ? num_splits : 0;
-#define IFB_RMS_CASE(IT) case IT: return rmsnorm_warp_launch<IT>(x, delta, ns, (size_t)split_stride, w, w_dtype, eps, out, out_dtype, rows, num_out_rows, stream);
-    switch (hidden / 128) {
+#define IFB_RMS_CASE(IT) case IT: return rmsnorm_block_launch<IT>(x, delta, ns, (size_t)split_stride, w, w_dtype, eps, out, out_dtype, rows, num_out_rows, hidden, stream);
+    switch ((hidden + 1023) / 1024) {
       IFB_RMS_CASE(1) IFB_RMS_CASE(2) IFB_RMS_CASE(3) IFB_RMS_CASE(4) IFB_RMS_CASE(5) IFB_RMS_CASE(6) IFB_RMS_CASE(7) IFB_RMS_CASE(8)
-      IFB_RMS_CASE(9) IFB_RMS_CASE(10) IFB_RMS_CASE(11) IFB_RMS_CASE(12) IFB_RMS_CASE(13) IFB_RMS_CASE(14) IFB_RMS_CASE(15) IFB_RMS_CASE(16)
     }
 #undef IFB_RMS_CASE
   }
@@ -374,20 +378,24 @@ qk_norm_rope_store_vec_kernel(T* __restrict__ qkv, int n_tokens, int nq, int nkv
   }
 }
 
-// The same for bfloat16 heads of 128 and steps of many tokens, where the bytes count: a warp takes one token, half a warp
-// one head at a time with 16 bytes (8 elements) per lane, so a token's 32 heads are 16 passes of which eight are
-// requested at once; the rotation partner of an element sits 8 lanes on.
+// The same for bfloat16 heads of 128 and steps of many tokens, where the bytes count: a warp takes 16 heads of one token,
+// half a warp one head at a time with 16 bytes (8 elements) per lane: eight passes, all requested at once; the rotation
+// partner of an element sits 8 lanes on.
 __global__ void __launch_bounds__(128)
 qk_norm_rope_store_d128_kernel(__nv_bfloat16* __restrict__ qkv, int n_tokens, int nq, int nkv, const void* __restrict__ qw,
                                const void* __restrict__ kw, int w_dtype, float eps, const float* __restrict__ rope_table,
                                const int* __restrict__ slots, __nv_bfloat16* __restrict__ pages, int page_size) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
-  constexpr int d = 128, B = 8;                                // B passes (two heads each) in flight
+#ifndef IFB_QK_B
+#define IFB_QK_B 4
+#endif
+  constexpr int d = 128, B = IFB_QK_B;                         // B passes (two heads each) in flight
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane >> 4, l16 = lane & 15;
-  const int tok = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int heads = nq + 2 * nkv, groups = (heads + 2 * B - 1) / (2 * B);      // a warp takes 16 heads of a token
+  const int item = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int tok = item / groups;
   if (tok >= n_tokens) return;
-  const int heads = nq + 2 * nkv;
   const int slot = slots ? slots[tok] : -1;
   float cs[8], sn[8];                                          // the angles of elements l16 * 8 .. + 7 of the first half
   if (rope_table) {
@@ -404,7 +412,8 @@ qk_norm_rope_store_d128_kernel(__nv_bfloat16* __restrict__ qkv, int n_tokens, in
   size_t page_base = 0;
   if (slot >= 0) page_base = (size_t)(slot / page_size) * 2 * nkv * page_size + (slot % page_size);
   __nv_bfloat16* row = qkv + (size_t)tok * heads * d;
-  for (int h0 = 0; h0 < heads; h0 += 2 * B) {
+  {
+    const int h0 = (item % groups) * 2 * B;
     uint4 in[B];
 #pragma unroll
     for (int b = 0; b < B; ++b) {
@@ -485,7 +494,8 @@ IFB_EXPORT int ifb_qk_norm_rope_store(void* qkv, int dtype, int n_tokens, int nq
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   if (d == 128 && dtype == IFB_BF16 && n_tokens >= 64 && (!inv_freq || (rotary_dim == d && !interleaved && rope_table)) &&
       ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)pages & 15) == 0)
-    return ifb_launch(qk_norm_rope_store_d128_kernel, dim3((unsigned)((n_tokens + warps - 1) / warps)), dim3(warps * 32), 0, stream,
+    return ifb_launch(qk_norm_rope_store_d128_kernel,
+                      dim3((unsigned)(((long long)n_tokens * ((nq + 2 * nkv + 2 * IFB_QK_B - 1) / (2 * IFB_QK_B)) + warps - 1) / warps)), dim3(warps * 32), 0, stream,
                       (__nv_bfloat16*)qkv, n_tokens, nq, nkv, qw, kw, w_dtype, eps, inv_freq ? rope_table : nullptr, slots,
                       (__nv_bfloat16*)pages, page_size);
   if ((d == 64 || d == 128 || d == 256) && (!inv_freq || (rotary_dim == d && !interleaved)) &&

@@ -83,7 +83,7 @@ __device__ __forceinline__ void gv_cluster_barrier() {
 // 2: a warp walks a long k range and keeps the memory pipe full while it multiplies (large models, where the
 // bytes count).
 template <int NB, int EPI, int WARPS, typename TO, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, (EPI == 4 && WARPS == 8) ? 2 : 1)
+__global__ void __launch_bounds__(WARPS * 32, (EPI == 4 && WARPS == 8) ? 2 : 0)
 linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* __restrict__ out, int n_rows, int o_out,
                    int k_dim, GvRowScale rs, GvResidual res, GvQkv qk) {
   extern __shared__ float gv_red[];                 // [WARPS][NE][NB*8][GV_ROWS], then [NB*8] row factors

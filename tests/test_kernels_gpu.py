@@ -87,7 +87,8 @@ def test_a_row_without_valid_logits_cannot_send_the_embedding_out_of_range(K):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("wdtype", DTYPES)
 @pytest.mark.parametrize("n,hidden,splits", [(1, 72, 0), (5, 1000, 1), (33, 3001, 3), (90, 1024, 1), (64, 128, 0), (70, 2048, 2),
-                                             (65, 640, 3), (3, 4096, 1)])
+                                             (65, 640, 3), (3, 4096, 1), (80, 4096, 1), (100, 5120, 2), (64, 8192, 0),
+                                             (70, 1000, 1), (66, 2052, 3), (64, 8196, 1)])
 def test_rmsnorm(K, dtype, wdtype, n, hidden, splits):
     x = rnd((n, hidden), torch.float32, 1)
     w = (1 + 0.1 * rnd((hidden,), torch.float32, 2)).to(wdtype)
