@@ -915,9 +915,12 @@ using SplitCfg = GemmCfg<0, 1, 128, 6>;
 // How many clusters of `splits` CTAs of that kernel the device holds at a time (0 if it cannot say): a product whose
 // tiles are no more than this runs in one wave.
 IFB_EXPORT int ifb_linear_tcgen05_split_clusters(int splits) {
-  static int cached[9] = {0};
-  static bool known[9] = {false};
-  if (splits < 2 || splits > 8) return 0;
+  static int cached_all[IFB_MAX_DEVICES][9] = {};
+  static bool known_all[IFB_MAX_DEVICES][9] = {};
+  int dev = 0;
+  if (splits < 2 || splits > 8 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= IFB_MAX_DEVICES) return 0;
+  int* cached = cached_all[dev];
+  bool* known = known_all[dev];
   if (!known[splits]) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 1, splits);
