@@ -557,11 +557,33 @@ def test_attention_on_tcgen05(K, nq, nkv, ps, window):
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2, atol=1.6e-2)
 
 
+@pytest.mark.parametrize("q_lens,seq_lens,window", [([1300], [1300], 0), ([2048], [2048], 0), ([700, 1216, 3], [900, 1216, 40], 0),
+                                                    ([1500], [1700], 300), ([1153], [1153], 0)])
+def test_attention_on_tcgen05_with_more_items_than_sms(K, q_lens, seq_lens, window):
+    """The kernel's grid is a CTA per SM; with more (query tile, kv head) items than SMs a CTA walks several, its
+    barriers' phases, score buffers and stages carrying on from one item to the next: items with an odd number of
+    key halves (the second stream skips the last tile), with a single half (the second stream has nothing), several
+    requests in one launch, portions deep inside a context, a window."""
+    nq, nkv, d, ps = 16, 8, 128, 16
+    qkv, kv, bt, cu, sl = _attention_case(torch.bfloat16, nq, nkv, d, ps, window, q_lens, seq_lens, 33, spike=(window == 0))
+    n = qkv.shape[0]
+    assert -(-max(q_lens) // 64) * nkv > K.sm_count
+    ref = torch.empty((n, nq * d), dtype=torch.bfloat16)
+    REF.paged_attention(qkv, nq, nkv, d, kv, bt, cu, sl, ref, d ** -0.5, window, max(q_lens), max(seq_lens))
+    for rep in range(2):
+        out = torch.full((n, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+        K.paged_attention(qkv.cuda(), nq, nkv, d, kv.cuda(), bt.cuda(), cu.cuda(), sl.cuda(), out, d ** -0.5, window,
+                          max(q_lens), max(seq_lens))
+        K.check_device_errors()
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1.6e-2, atol=1.6e-2)
+
+
 @pytest.mark.parametrize("q_len", [65, 100, 105, 127, 128, 200])
-def test_attention_on_tcgen05_second_query_tile_waits_for_its_products(K, q_len):
-    """A CTA's second query tile that works through exactly two halves of keys reads its accumulator after a wait by
-    parity on the barrier of its P V products; a step that skipped the wait for the first half's products left that
-    wait one phase short, and it passed while the products were still in flight whenever the values arrived late.
+def test_attention_on_tcgen05_waits_for_its_products(K, q_len):
+    """A stream that works through exactly two halves of keys reads its accumulator after a wait by parity on the
+    barrier of its P V products; a step that skipped the wait for the first half's products left that wait one phase
+    short, and it passed while the products were still in flight whenever the values arrived late (found when a
+    CTA's second query tile had two halves; the lengths here give one and two halves per stream and tile).
     The kernel is run many times on fresh, differently placed inputs; every run must agree with the plain statement."""
     nq, nkv, d, ps = 16, 8, 128, 16
     for rep in range(12):
