@@ -33,6 +33,12 @@ def _ptr(t):
     return 0 if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+if _raw_stream is None:                       # an older torch: the public, slower way
+    def _raw_stream(device_index):
+        return torch.cuda.current_stream(device_index).cuda_stream
+
+
 def _check(status, what):
     if status == 0:
         return
@@ -117,6 +123,8 @@ class CudaKernels:
         self.tc_split_min_rows = int(os.environ.get("INFURNACE_TC_SPLIT_MIN_ROWS", "0"))     # 0: by the matrix
         self.tc_fold_max_rows = int(os.environ.get("INFURNACE_TC_FOLD_MAX_ROWS", "128"))
         self._tc_clusters = {}         # CTAs per cluster -> clusters of the split product that run at a time
+        self._route_memo = {}          # what _on_tcgen05 and tcgen05_splits answered (asked several times per launch)
+        self._splits_memo = {}
         self._attn_mma = {}        # head size -> library
         self._attn_scratch = None
         self._attn_counters = None
@@ -128,7 +136,9 @@ class CudaKernels:
 
     @staticmethod
     def _stream():
-        return torch.cuda.current_stream().cuda_stream
+        # the raw handle of torch's current stream on the current device (torch.cuda.current_stream() builds a Stream
+        # object around it on every call, which was a fifth of an eager step's host time)
+        return _raw_stream(torch._C._cuda_getDevice())
 
     # ------------------------------------------------------------------ embedding
     def embed(self, table, ids, out):
@@ -206,6 +216,13 @@ class CudaKernels:
                                          n, o, k, epi, self._stream()), "linear")
 
     def _on_tcgen05(self, n, w, epilogue="none", shared_k=True):
+        key = (n, w.shape[0], w.shape[1], w.dtype, epilogue, shared_k)
+        hit = self._route_memo.get(key)
+        if hit is None:
+            hit = self._route_memo[key] = self._on_tcgen05_rule(n, w, epilogue, shared_k)
+        return hit
+
+    def _on_tcgen05_rule(self, n, w, epilogue, shared_k):
         """Which kernel a bfloat16 product of n rows against w runs on.  More than 64 rows: the tcgen05 kernel.
         From ``tc_split_min_rows`` rows, a product with the plain epilogue whose few tiles can share their k
         range in clusters (:meth:`tcgen05_splits`): the tcgen05 kernel in that form, which streams a long k
@@ -269,6 +286,13 @@ class CudaKernels:
         """How many CTAs (a cluster) share the k range of a tile in the tcgen05 product of up to 512 rows
         (128 with the silu_gate epilogue): the most, up to 8, whose clusters for all tiles of 128 x 128
         run at the same time, each CTA with at least ``tc_split_min_k`` of k; 1 if that is none."""
+        key = (n, o, k, bool(epi))
+        hit = self._splits_memo.get(key)
+        if hit is None:
+            hit = self._splits_memo[key] = self._tcgen05_splits_rule(n, o, k, epi)
+        return hit
+
+    def _tcgen05_splits_rule(self, n, o, k, epi):
         if n > (128 if epi else 512):
             return 1
         tiles = -(-o // 128) * -(-n // 128)
