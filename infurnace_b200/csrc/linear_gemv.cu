@@ -42,7 +42,8 @@ struct GvResidual {        // producer side, epilogue 2
   const void* g;           // [o_out] norm weight
   int g_dtype;
   float* partials;         // [gridDim.x][n_rows], written
-};
+  int feat;                // features per CTA for the plain epilogue and epilogue 2: 16, or 8 (the tile's rows 8-15 stay
+};                         // empty) where 16 would leave more than half of the SMs without a CTA
 
 // EPI 3: the product is the fused q | k | v projection of an attention layer and the kernel finishes what follows it for
 // every head: RMSNorm over the head (q and k heads), rotation in the half-split pairing, q written to the qkv row, k and v
@@ -96,7 +97,9 @@ linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* _
   // their rotation partners head_dim/2 further on
   const int qk_per_head = EPI == 3 ? qk.head_dim / 32 : 1;
   const int qk_head = EPI == 3 ? blockIdx.x / qk_per_head : 0, qk_c = EPI == 3 ? blockIdx.x % qk_per_head : 0;
-  const int o0 = EPI == 3 ? qk_head * qk.head_dim + qk_c * GV_ROWS : blockIdx.x * (EPI == 4 ? 8 : GV_ROWS), n0 = blockIdx.y * (NB * 8);
+  const bool half_tile = (EPI == 0 || EPI == 2) && res.feat == 8;     // 8 features per CTA: no weight rows for the tile's second half
+  const int feat = (EPI == 4 || half_tile) ? 8 : GV_ROWS;
+  const int o0 = EPI == 3 ? qk_head * qk.head_dim + qk_c * GV_ROWS : blockIdx.x * feat, n0 = blockIdx.y * (NB * 8);
   const int second = EPI == 3 ? qk.head_dim / 2 : o_out;      // distance of the second set of 16 weight rows from the first
   const int kw = ((k_dim + WARPS - 1) / WARPS + 127) / 128 * 128;      // k per warp, whole 128-wide steps
   const int kbeg = warp * kw, kend = min(k_dim, kbeg + kw);
@@ -137,7 +140,7 @@ linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* _
 #pragma unroll
         for (int e = 0; e < NE; ++e) {
           wa[e][c] = in ? gv_ld_stream16(wrow[e][0] + k) : make_uint4(0, 0, 0, 0);
-          wb[e][c] = in ? gv_ld_stream16(wrow[e][1] + k) : make_uint4(0, 0, 0, 0);
+          wb[e][c] = (in && !half_tile) ? gv_ld_stream16(wrow[e][1] + k) : make_uint4(0, 0, 0, 0);
         }
       }
       if (!waited) {           // the weights are on their way; now wait for whoever writes x
@@ -180,7 +183,7 @@ linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* _
   #pragma unroll
         for (int e = 0; e < NE; ++e) {
           wa[st][e][c] = in ? gv_ld_stream16(wrow[e][0] + k) : make_uint4(0, 0, 0, 0);
-          wb[st][e][c] = in ? gv_ld_stream16(wrow[e][1] + k) : make_uint4(0, 0, 0, 0);
+          wb[st][e][c] = (in && !half_tile) ? gv_ld_stream16(wrow[e][1] + k) : make_uint4(0, 0, 0, 0);
         }
       }
     };
@@ -280,7 +283,7 @@ linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* _
   for (int idx = tid; idx < NB * 8 * GV_ROWS; idx += WARPS * 32) {
     const int n = idx / GV_ROWS, m = idx % GV_ROWS;
     const int o = o0 + m, tok = n0 + n;
-    const bool valid = o < o_out && tok < n_rows;
+    const bool valid = o < o_out && tok < n_rows && (!half_tile || m < 8);
     float y[NE];
 #pragma unroll
     for (int e = 0; e < NE; ++e) {
@@ -365,18 +368,38 @@ linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* _
   }
 }
 
+// Features per CTA of the plain epilogue and epilogue 2: 8 for a single row where tiles of 16 would leave more than
+// half of the SMs without a CTA (the o and down products of a small model: 1,024 features are 64 CTAs of 16, each
+// pulling twice the bytes a CTA of 8 pulls, on a device of 148 SMs).  Measured in a decode step of the 0.6B sizes:
+// 0.802 to 0.787 ms at one row; with 2, 4 and 8 rows the 128 CTAs' reads of the rows outweigh it (0.894 to 0.948,
+// 1.020 to 1.117, 1.314 to 1.374 ms), so those keep 16.
+static int gv_features_per_cta(int o, int n_rows) {
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      sm_count = 1;
+  }
+  static int forced = -1;                    // IFB_GV_FEAT=16 keeps tiles of 16 (for measurements)
+  if (forced < 0) { const char* v = getenv("IFB_GV_FEAT"); forced = v ? atoi(v) : 0; }
+  if (forced == 16 || n_rows > 1) return GV_ROWS;
+  return 2 * ((o + GV_ROWS - 1) / GV_ROWS) <= sm_count ? 8 : GV_ROWS;
+}
+
 template <int NB, int EPI, int WARPS, typename TO, int STAGES = 1>
 static int gv_launch(const void* x, const void* w, void* out, int n, int o, int k, const GvRowScale& rs, const GvResidual& res,
                      cudaStream_t s) {
   static_assert(EPI != 3, "the fused qkv epilogue is launched by gv_launch_qkv");
   const size_t smem = ((size_t)WARPS * (EPI == 1 ? 2 : 1) * NB * 8 * GV_ROWS + NB * 8) * sizeof(float);
   IFB_ALLOW_SMEM((linear_gemv_kernel<NB, EPI, WARPS, TO, STAGES>), smem);
-  constexpr int PER_CTA = EPI == 4 ? 8 : GV_ROWS;
-  dim3 grid((o + PER_CTA - 1) / PER_CTA, (n + NB * 8 - 1) / (NB * 8));
+  GvResidual res_f = res;
+  res_f.feat = (EPI == 0 || EPI == 2) ? gv_features_per_cta(o, n) : GV_ROWS;
+  const int per_cta = EPI == 4 ? 8 : res_f.feat;
+  dim3 grid((o + per_cta - 1) / per_cta, (n + NB * 8 - 1) / (NB * 8));
   // matrices beyond GV_EARLY_BYTES are streamed; a launch ahead of the predecessor's end costs them more than it hides
   const bool early = (size_t)o * k * ((EPI == 1 || EPI == 4) ? 4 : 2) <= GV_EARLY_BYTES;
   return ifb_launch_opt(early, linear_gemv_kernel<NB, EPI, WARPS, TO, STAGES>, grid, dim3(WARPS * 32), smem, s, (const bf16*)x,
-                        (const bf16*)w, (TO*)out, n, o, k, rs, res, GvQkv{});
+                        (const bf16*)w, (TO*)out, n, o, k, rs, res_f, GvQkv{});
 }
 
 // The fused q | k | v product: one CTA per (head, 16 feature pairs), the CTAs of a head as a thread-block cluster.
@@ -513,12 +536,15 @@ IFB_EXPORT int ifb_linear_gemv_qkv(const void* x, const void* w, void* qkv, int 
                  : gv_launch_qkv<2, 8, 2>(x, w, qkv, n_rows, k_dim, rs, qk, stream);
 }
 
-// How many partial sums per row ifb_linear_gemv_residual_norm writes for this many output features.
-IFB_EXPORT int ifb_linear_gemv_parts(int out_features) { return (out_features + GV_ROWS - 1) / GV_ROWS; }
+// How many partial sums per row ifb_linear_gemv_residual_norm writes for this many output features and rows.
+IFB_EXPORT int ifb_linear_gemv_parts(int out_features, int n_rows) {
+  const int feat = gv_features_per_cta(out_features, n_rows);
+  return (out_features + feat - 1) / feat;
+}
 
 // The product with the residual addition and the weight of the norm that follows folded in: v = resid + a w^T is
 // written back to resid (float32 [n_rows, out_features]), out = v * g in bfloat16, and partials[p][n] = the sum of
-// v[n][f]^2 over the 16 features f of part p (ifb_linear_gemv_parts(out_features) parts).  A later ifb_linear_gemv with
+// v[n][f]^2 over the 16 (or 8) features f of part p (ifb_linear_gemv_parts(out_features, n_rows) parts).  A later ifb_linear_gemv with
 // these partials as its scale completes the RMSNorm.
 IFB_EXPORT int ifb_linear_gemv_residual_norm(const void* a, const void* w, float* resid, const void* g, int g_dtype,
                                              void* out, float* partials, int n_rows, int out_features, int k_dim,

@@ -350,7 +350,7 @@ class CudaKernels:
         if n is not None and w is not None and self._on_tcgen05(n, w):
             splits = self.tcgen05_splits(n, w.shape[0], w.shape[1])
             return int(self._tc_lib().ifb_linear_tcgen05_fold_parts(int(n), int(out_features), int(splits)))
-        return int(self.core.ifb_linear_gemv_parts(int(out_features)))
+        return int(self.core.ifb_linear_gemv_parts(int(out_features), int(n) if n is not None else 1 << 20))
 
     def linear_residual_norm(self, a, w, x, norm_weight, out, partials):
         """x += a w^T (x float32, in place); out = x * norm_weight (bfloat16); partials[p, n] = the sum

@@ -472,7 +472,7 @@ def _folded_norm_case(K, n, hidden, inner, width2, epilogue, gdt):
     assert K.can_fold_norm(n, torch.bfloat16, w2d, epilogue) and K.can_fold_norm(n, torch.bfloat16, w1d)
     parts = K.fold_parts(hidden, n, w1d)
     if not K._on_tcgen05(n, w1d):
-        assert parts == -(-hidden // 16)
+        assert parts in (-(-hidden // 16), -(-hidden // 8))     # a CTA of the few-rows kernel takes 16 features, or 8 of a narrow product
     xd = x.cuda()
     vals = torch.full((n, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
     partials = torch.full((parts, n), float("nan"), dtype=torch.float32, device="cuda")
