@@ -15,6 +15,12 @@
 
 typedef __nv_bfloat16 bf16;
 constexpr int GV_ROWS = 16;
+// CTAs per SM asked of the compiler for the plain one-stage kernel of 8 warps and one block of tokens (the LM head of a
+// small model, 9,496 CTAs): with 80 registers three fit and the 311 MB stream at 5.8 to 6.3 TB/s; with the 103 the
+// compiler took unasked two fit (4.8 to 5.0 TB/s), with four (64 registers, spills) it is slower again.
+#ifndef IFB_GV_LM_BLOCKS
+#define IFB_GV_LM_BLOCKS 3
+#endif
 constexpr size_t GV_EARLY_BYTES = 24u << 20;     // weight bytes up to which a launch may start before its predecessor ends
 
 __device__ __forceinline__ uint4 gv_ld_stream16(const void* p) {
@@ -84,7 +90,7 @@ __device__ __forceinline__ void gv_cluster_barrier() {
 // 2: a warp walks a long k range and keeps the memory pipe full while it multiplies (large models, where the
 // bytes count).
 template <int NB, int EPI, int WARPS, typename TO, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, (EPI == 4 && WARPS == 8) ? 2 : 0)
+__global__ void __launch_bounds__(WARPS * 32, (EPI == 4 && WARPS == 8) ? 2 : (EPI == 0 && WARPS == 8 && STAGES == 1 && NB == 1) ? IFB_GV_LM_BLOCKS : 0)
 linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* __restrict__ out, int n_rows, int o_out,
                    int k_dim, GvRowScale rs, GvResidual res, GvQkv qk) {
   extern __shared__ float gv_red[];                 // [WARPS][NE][NB*8][GV_ROWS], then [NB*8] row factors
