@@ -243,15 +243,15 @@ class CudaKernels:
         """From how many rows the tcgen05 kernel with a shared k range beats the few-rows kernel, by
         measurement in a step's graph (o and down products of the 0.6B, 8B and 32B sizes): 17 for a small
         matrix (the few-rows kernel is bound by its round trips, not by its bytes); 9 for a large one (a
-        second block of 8 rows costs the few-rows kernel a third more); 2 where the few-rows kernel with
+        second block of 8 rows costs the few-rows kernel a third more); 1 where the few-rows kernel with
         its one CTA of 16 features per SM (long k) leaves most of its last wave empty (5,120 features:
-        320 CTAs on 148 SMs)."""
+        320 CTAs on 148 SMs; a decode step of one row of the 32B sizes 14.13 against 13.74 ms)."""
         if self.tc_split_min_rows:
             return self.tc_split_min_rows
         o, k = w.shape
         waves = -(-o // 16) / self.sm_count
         if k > 3072 and -(-waves // 1) / waves > 1.25:
-            return 2
+            return 1
         return 9 if w.numel() >= (1 << 23) else 17
 
     def _linear_tcgen05(self, x, w, out, n, o, k, epi, shape=0, splits=1, row_scale=None, residual=None):
