@@ -76,9 +76,11 @@ __device__ __forceinline__ bool tc_mbar_try_wait(uint64_t* bar, uint32_t parity)
   return ok != 0;
 }
 __device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+  unsigned long long t0 = 0;
   for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
     if (tc_mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
+    if (ifb_wait_expired(i, t0)) break;
   }
   *abort_flag = 1;
   atomicExch(err, code);

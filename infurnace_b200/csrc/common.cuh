@@ -41,6 +41,18 @@ __device__ __forceinline__ void ifb_pdl_wait() { asm volatile("griddepcontrol.wa
 __device__ __forceinline__ void ifb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void ifb_prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p)); }
 
+// A bound in time for polled waits, beside their bound in polls (a poll of an mbarrier may itself block for a while, so
+// a count of polls bounds nothing in seconds): true once more than IFB_WAIT_LIMIT_NS have passed since the wait's first
+// look at the clock.  The clock is read every 256 polls; t0 starts as 0.
+constexpr unsigned long long IFB_WAIT_LIMIT_NS = 2000000000ull;      // two seconds: a thousand times the longest honest wait
+__device__ __forceinline__ bool ifb_wait_expired(uint32_t poll, unsigned long long& t0) {
+  if ((poll & 255u) != 255u) return false;
+  unsigned long long now;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+  if (t0 == 0) { t0 = now; return false; }
+  return now - t0 > IFB_WAIT_LIMIT_NS;
+}
+
 static inline bool ifb_pdl_enabled() {
   static int on = -1;
   if (on < 0) { const char* e = getenv("IFB_PDL"); on = (e && e[0] == '0') ? 0 : 1; }
